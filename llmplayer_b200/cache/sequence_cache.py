@@ -34,6 +34,14 @@ class KVRequest:
 
 
 @dataclass(frozen=True)
+class RowsRequest:
+    """One row of ``width`` values for every position (or a window of positions) of a sequence: what a
+    mixer keeps that attends over something other than per-head keys and values (a shared latent, say)."""
+    width: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
 class StateRequest:
     """A block of fixed shape per sequence, zero at the sequence's start."""
     shape: Tuple[int, ...]
@@ -41,24 +49,28 @@ class StateRequest:
 
 
 class KVGroup:
-    """Storage of the runs that share one :class:`KVRequest`.
+    """Storage of the runs that share one paged request.
 
-    ``storage[i]`` is the tensor of the i-th run of the group:
-    [num_pages, 2 (keys, values), kv heads, PAGE_SIZE, head_dim].
+    ``storage[i]`` is the tensor of the i-th run of the group: for a :class:`KVRequest`
+    [num_pages, 2 (keys, values), kv heads, PAGE_SIZE, head_dim], for a :class:`RowsRequest`
+    [num_pages, PAGE_SIZE, width].
     """
 
-    def __init__(self, request: KVRequest, runs: Sequence[int], num_pages: int, dtype: torch.dtype, device):
+    def __init__(self, request, runs: Sequence[int], num_pages: int, dtype: torch.dtype, device):
         self.request = request
         self.runs = list(runs)
         self.pages = PageMap(num_pages, window=request.window)
+        if isinstance(request, RowsRequest):
+            page_shape = (PAGE_SIZE, request.width)
+        else:
+            page_shape = (2, request.num_kv_heads, PAGE_SIZE, request.head_dim)
         # zeros once, so that stale rows are always finite; never cleared again
-        self.storage = torch.zeros(
-            (len(self.runs), num_pages, 2, request.num_kv_heads, PAGE_SIZE, request.head_dim),
-            dtype=dtype, device=device)
+        self.storage = torch.zeros((len(self.runs), num_pages) + page_shape, dtype=dtype, device=device)
 
     def bytes_per_token(self) -> int:
         r = self.request
-        return len(self.runs) * 2 * r.num_kv_heads * r.head_dim * self.storage.element_size()
+        per = r.width if isinstance(r, RowsRequest) else 2 * r.num_kv_heads * r.head_dim
+        return len(self.runs) * per * self.storage.element_size()
 
     def view_of(self, run: int) -> torch.Tensor:
         return self.storage[self.runs.index(run)]
@@ -94,9 +106,9 @@ class SequenceCache:
         self._length: Dict[int, int] = {}
         self.groups: List[KVGroup] = []
         self._views: List[object] = [None] * len(requests)
-        by_request: Dict[KVRequest, List[int]] = {}
+        by_request: Dict[object, List[int]] = {}
         for run, req in enumerate(requests):
-            if isinstance(req, KVRequest):
+            if isinstance(req, (KVRequest, RowsRequest)):
                 by_request.setdefault(req, []).append(run)
         for req, runs in by_request.items():
             group = KVGroup(req, runs, self.num_pages, kv_dtype, device)
@@ -109,7 +121,7 @@ class SequenceCache:
                 rows = torch.zeros((self.max_slots,) + tuple(req.shape), dtype=req.dtype, device=device)
                 self._state_rows.append(rows)
                 self._views[run] = StateView(rows)
-            elif req is not None and not isinstance(req, KVRequest):
+            elif req is not None and not isinstance(req, (KVRequest, RowsRequest)):
                 raise CacheError(f"run {run}: unknown cache request {req!r}")
 
     # ------------------------------------------------------------------ slots

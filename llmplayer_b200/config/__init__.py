@@ -4,8 +4,9 @@ from .registry import (
     register_architecture, unregister_architecture,
 )
 from .llama import LlamaConfig
+from .ramupel import RamupelConfig
 
 __all__ = [
-    "ArchitectureConfig", "LlamaConfig", "config_class_for", "config_from_dict",
+    "ArchitectureConfig", "LlamaConfig", "RamupelConfig", "config_class_for", "config_from_dict",
     "known_architectures", "load_config", "register_architecture", "unregister_architecture",
 ]

@@ -75,9 +75,13 @@ def config_from_dict(raw: dict) -> ArchitectureConfig:
     if not isinstance(raw, dict):
         raise ConfigError("config.json must hold a JSON object")
     archs = raw.get("architectures")
-    if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError('config.json needs "architectures": ["<name>"]')
-    return config_class_for(archs[0]).from_dict(raw)
+    if isinstance(archs, list) and archs and isinstance(archs[0], str):
+        name = archs[0]
+    elif isinstance(raw.get("architecture"), str) and raw["architecture"]:
+        name = raw["architecture"]                 # some designs name themselves with one string
+    else:
+        raise ConfigError('config.json needs "architectures": ["<name>"] or "architecture": "<name>"')
+    return config_class_for(name).from_dict(raw)
 
 
 def load_config(model_dir: str) -> ArchitectureConfig:

@@ -10,26 +10,31 @@
 // ---------------------------------------------------------------- embedding
 template <typename TW>
 __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
-                             float* __restrict__ out, int d) {
+                             float* __restrict__ out, int d, float scale) {
     lp_grid_release();
     lp_grid_wait();
     const int t = blockIdx.x;
     const long long row = tokens[t];
     const TW* src = table + row * d;
     float* dst = out + (long long)t * d;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = lp_to_float(src[i]);
+    // a scale of one leaves the row as stored (no multiplication, the same bits)
+    if (scale == 1.0f) {
+        for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = lp_to_float(src[i]);
+    } else {
+        for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = lp_to_float(src[i]) * scale;
+    }
 }
 
 extern "C" int lp_embed(const void* table, int table_dtype, const int* tokens, float* out, int T, int d,
-                        cudaStream_t stream) {
+                        float scale, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (d <= 0) LP_REFUSE("embed: width %d", d);
     const int threads = d >= 1024 ? 256 : 128;
     // the embedding opens a step: it is launched without the early start (see lp_launch_first)
     if (table_dtype == LP_F32)
-        lp_launch_first(embed_kernel<float>, T, threads, 0, stream, (const float*)table, tokens, out, d);
+        lp_launch_first(embed_kernel<float>, T, threads, 0, stream, (const float*)table, tokens, out, d, scale);
     else if (table_dtype == LP_BF16)
-        lp_launch_first(embed_kernel<__nv_bfloat16>, T, threads, 0, stream, (const __nv_bfloat16*)table, tokens, out, d);
+        lp_launch_first(embed_kernel<__nv_bfloat16>, T, threads, 0, stream, (const __nv_bfloat16*)table, tokens, out, d, scale);
     else
         LP_REFUSE("embed: table dtype code %d", table_dtype);
     return lp_check_launch("embed");
@@ -391,6 +396,134 @@ extern "C" int lp_rope_cache_write(const float* qkv, int ld, const float* inv_fr
     else LP_REFUSE("rope_cache_write: dtype codes q=%d kv=%d", q_dtype, kv_dtype);
 #undef LP_LAUNCH_ROPE
     return lp_check_launch("rope_cache_write");
+}
+
+// ---------------------------------------------------------------- layer norm (gain, no bias)
+// out[r, i] = (x[row(r), i] - mean) / sqrt(var + eps) * w[i], var = mean of the squared deviations
+// from the mean; one block per row, three passes over a row that stays in L1 (sum, squared
+// deviations, write), all float32, every sum in a fixed order.
+template <typename TOut>
+__global__ void __launch_bounds__(NORM_THREADS)
+layernorm_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
+                 TOut* __restrict__ out, int d, float eps) {
+    __shared__ float scratch[32];
+    lp_grid_release();
+    lp_grid_wait();
+    const int r = blockIdx.x;
+    const long long src = rows ? rows[r] : r;
+    const float* xr = x + src * d;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < d; i += NORM_THREADS) s += xr[i];
+    const float mean = lp_block_sum(s, scratch) / (float)d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += NORM_THREADS) {
+        const float c = xr[i] - mean;
+        ss += c * c;
+    }
+    const float var = lp_block_sum(ss, scratch) / (float)d;
+    const float scale = 1.0f / sqrtf(var + eps);
+    TOut* o = out + (long long)r * d;
+    for (int i = threadIdx.x; i < d; i += NORM_THREADS) o[i] = lp_from_float<TOut>((xr[i] - mean) * scale * w[i]);
+}
+
+extern "C" int lp_layernorm(const float* x, const int* rows, const float* w, void* out, int out_dtype, int R, int d,
+                            float eps, cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (d <= 0) LP_REFUSE("layernorm: width %d", d);
+    if (out_dtype == LP_F32)
+        lp_launch(layernorm_kernel<float>, R, NORM_THREADS, 0, stream, x, rows, w, (float*)out, d, eps);
+    else if (out_dtype == LP_BF16)
+        lp_launch(layernorm_kernel<__nv_bfloat16>, R, NORM_THREADS, 0, stream, x, rows, w, (__nv_bfloat16*)out, d, eps);
+    else
+        LP_REFUSE("layernorm: output dtype code %d", out_dtype);
+    return lp_check_launch("layernorm");
+}
+
+// ---------------------------------------------------------------- xIELU activation
+// act(z) = softplus(p) z^2 + z / 2 for z > 0, (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2 otherwise; p and q are
+// the two learned numbers `pq` of the layer. z: float32 [T, ldz] (a slice of a wider product), out: [T, F].
+__device__ __forceinline__ float lp_softplus(float v) { return fmaxf(v, 0.f) + log1pf(expf(-fabsf(v))); }
+
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+xielu_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ pq, TOut* __restrict__ out, int T, int F) {
+    lp_grid_release();
+    lp_grid_wait();
+    const float ap = lp_softplus(pq[0]), an = 0.5f + lp_softplus(pq[1]);
+    const long long n = (long long)T * F;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / F;
+        const int f = (int)(i - t * F);
+        const float v = z[t * ldz + f];
+        const float a = v > 0.f ? ap * v * v + 0.5f * v : an * (expm1f(v) - v) + 0.5f * v;
+        out[i] = lp_from_float<TOut>(a);
+    }
+}
+
+extern "C" int lp_xielu(const float* z, int ldz, const float* pq, void* out, int out_dtype, int T, int F,
+                        cudaStream_t stream) {
+    if (T <= 0 || F <= 0) return 0;
+    if (ldz < F) LP_REFUSE("xielu: rows of %d values for %d features", ldz, F);
+    const long long n = (long long)T * F;
+    long long blocks = (n + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (out_dtype == LP_F32) lp_launch(xielu_kernel<float>, (unsigned)blocks, 256, 0, stream, z, ldz, pq, (float*)out, T, F);
+    else if (out_dtype == LP_BF16)
+        lp_launch(xielu_kernel<__nv_bfloat16>, (unsigned)blocks, 256, 0, stream, z, ldz, pq, (__nv_bfloat16*)out, T, F);
+    else LP_REFUSE("xielu: output dtype code %d", out_dtype);
+    return lp_check_launch("xielu");
+}
+
+// ---------------------------------------------------------------- gated residual sum and weighted sum over depth
+// y[t, i] = x[t, i] + a[t, i] * sigmoid(ga[t, i] + ba[i]) + b[t, i] * sigmoid(gb[t, i] + bb[i])
+// (a gate pointer that is null leaves its branch ungated, a branch pointer that is null leaves it out), all float32.
+// With `streams` [count, T, d]: y is kept as stream `count - 1`, and x <- sum_j mix[j] * streams[j] over
+// j = 0 .. count - 1 in increasing j; without, x <- y. `keep_input`: the incoming x is stream `count - 2` and is
+// stored there first (the first layer of a model, whose input is the embedding's output).
+__global__ void __launch_bounds__(256)
+gated_sum_kernel(float* __restrict__ x, const float* __restrict__ a, const float* __restrict__ ga, int ldga,
+                 const float* __restrict__ ba, const float* __restrict__ b, const float* __restrict__ gb, int ldgb,
+                 const float* __restrict__ bb, float* __restrict__ streams, const float* __restrict__ mix, int count,
+                 int keep_input, int T, int d) {
+    lp_grid_release();
+    lp_grid_wait();
+    const long long n = (long long)T * d;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / d;
+        const int c = (int)(i - t * d);
+        float y = x[i];
+        if (streams && keep_input) streams[(long long)(count - 2) * n + i] = y;
+        if (a) {
+            float v = a[i];
+            if (ga) v *= 1.0f / (1.0f + expf(-(ga[t * ldga + c] + (ba ? ba[c] : 0.f))));
+            y += v;
+        }
+        if (b) {
+            float v = b[i];
+            if (gb) v *= 1.0f / (1.0f + expf(-(gb[t * ldgb + c] + (bb ? bb[c] : 0.f))));
+            y += v;
+        }
+        if (streams) {
+            streams[(long long)(count - 1) * n + i] = y;
+            float s = 0.f;
+            for (int j = 0; j + 1 < count; ++j) s = fmaf(mix[j], streams[(long long)j * n + i], s);
+            y = fmaf(mix[count - 1], y, s);
+        }
+        x[i] = y;
+    }
+}
+
+extern "C" int lp_gated_sum(float* x, const float* a, const float* ga, int ldga, const float* ba, const float* b,
+                            const float* gb, int ldgb, const float* bb, float* streams, const float* mix, int count,
+                            int keep_input, int T, int d, cudaStream_t stream) {
+    if (T <= 0 || d <= 0) return 0;
+    if (streams && (count < 1 || !mix)) LP_REFUSE("gated_sum: %d streams without weights", count);
+    if (streams && keep_input && count < 2) LP_REFUSE("gated_sum: no place for the input among %d streams", count);
+    const long long n = (long long)T * d;
+    long long blocks = (n + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    lp_launch(gated_sum_kernel, (unsigned)blocks, 256, 0, stream, x, a, ga, ldga, ba, b, gb, ldgb, bb, streams, mix, count, keep_input, T, d);
+    return lp_check_launch("gated_sum");
 }
 
 // ---------------------------------------------------------------- rotation angles of a step's tokens

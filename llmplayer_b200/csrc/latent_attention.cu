@@ -1,0 +1,415 @@
+// Attention over a cache of low-rank latents ("latent attention").
+//
+// Every position of a sequence keeps one row [rank + dr]: the normed latent c (rank values) from which
+// each head's keys and values are linear maps (K_h = U_h c, V_h = W_h c), and one rotated key part (dr
+// values) that all heads share. A head's score against a position is
+//     (q_n . U_h c + q_r . k_r) * scale  =  ((U_h^T q_n) . c + q_r . k_r) * scale,
+// so the key map is applied to the query once ("absorbed") and every head attends over the same rows,
+// and the head's output W_h (sum_j p_j c_j) applies the value map once to the weighted latent sum.
+//
+//   lp_latent_prepare   per token: RMS norm of the latent, rotation of the shared key part and of the
+//                       queries' rotated parts, write of the row into the paged cache
+//   lp_latent_absorb    q'[t, h] = [U_h^T q_n | q_r]
+//   lp_latent_attend    online-softmax attention of q' over the rows of the pages (float32 scores,
+//                       weights and sums), the keys of a sequence optionally shared out over several CTAs
+//   lp_latent_expand    merge of the shares, value map, output gate
+//
+// All arithmetic is float32; the cache and the weights may be bfloat16 or float32. Keys are visited in
+// blocks of 32 aligned to absolute positions, so a position's result does not depend on how its
+// sequence was cut into steps or batched (the number of shares changes only the last merge).
+#include "common.cuh"
+
+namespace {
+
+constexpr int KEYS = 32;            // keys per block: one per lane
+constexpr int WARPS = 8;
+
+// ---------------------------------------------------------------- prepare
+template <typename TKV>
+__global__ void __launch_bounds__(256)
+latent_prepare_kernel(const float* __restrict__ proj, int ld, int q_off, int kv_off, const float* __restrict__ gain,
+                      float eps, const float* __restrict__ inv_freq, int rot, const int* __restrict__ positions,
+                      const int* __restrict__ seq_ids, const int* __restrict__ page_table, int pt_stride,
+                      float* __restrict__ q_out, TKV* __restrict__ pages, int H, int dn, int dr, int rank,
+                      int page_size) {
+    __shared__ float cs[128], sn[128];
+    __shared__ float scratch[32];
+    lp_grid_release();
+    lp_grid_wait();
+    const int t = blockIdx.x, tid = threadIdx.x;
+    const int pos = positions[t];
+    const int half = rot >> 1;
+    for (int i = tid; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &sn[i], &cs[i]);
+    const float* row = proj + (long long)t * ld;
+    const float* kv = row + kv_off;
+    float ss = 0.f;
+    for (int i = tid; i < rank; i += blockDim.x) ss += kv[i] * kv[i];
+    ss = lp_block_sum(ss, scratch);                       // also publishes cs / sn
+    const float factor = 1.0f / sqrtf(ss / (float)rank + eps);
+    const int page = page_table[(long long)seq_ids[t] * pt_stride + pos / page_size];
+    const int Dk = rank + dr;
+    TKV* dst = pages + ((long long)page * page_size + pos % page_size) * Dk;
+    for (int i = tid; i < rank; i += blockDim.x) dst[i] = lp_from_float<TKV>(kv[i] * factor * gain[i]);
+    // the shared key part: pairs (i, i + half) of its first `rot` values turn, the rest pass
+    const float* kr = kv + rank;
+    for (int i = tid; i < dr; i += blockDim.x) {
+        float v = kr[i];
+        if (i < half) v = __fsub_rn(__fmul_rn(kr[i], cs[i]), __fmul_rn(kr[i + half], sn[i]));
+        else if (i < rot) v = __fadd_rn(__fmul_rn(kr[i], cs[i - half]), __fmul_rn(kr[i - half], sn[i - half]));
+        dst[rank + i] = lp_from_float<TKV>(v);
+    }
+    // queries: head by head [dn as projected | dr with the same rotation]
+    const int hd = dn + dr;
+    const float* q = row + q_off;
+    float* qo = q_out + (long long)t * H * hd;
+    for (int e = tid; e < H * hd; e += blockDim.x) {
+        const int i = e % hd - dn;
+        float v = q[e];
+        if (i >= 0) {
+            if (i < half) v = __fsub_rn(__fmul_rn(q[e], cs[i]), __fmul_rn(q[e + half], sn[i]));
+            else if (i < rot) v = __fadd_rn(__fmul_rn(q[e], cs[i - half]), __fmul_rn(q[e - half], sn[i - half]));
+        }
+        qo[e] = v;
+    }
+}
+
+// ---------------------------------------------------------------- absorb
+constexpr int TOK_TILE = 8;
+
+template <typename TW>
+__global__ void __launch_bounds__(128)
+latent_absorb_kernel(const float* __restrict__ q, const TW* __restrict__ uk, float* __restrict__ qa, int T, int H,
+                     int dn, int dr, int rank) {
+    extern __shared__ float qs[];                         // [TOK_TILE][dn]
+    lp_grid_release();
+    lp_grid_wait();
+    const int t0 = blockIdx.x * TOK_TILE, h = blockIdx.y, tid = threadIdx.x;
+    const int hd = dn + dr, Dk = rank + dr;
+    const int nt = min(TOK_TILE, T - t0);
+    for (int e = tid; e < TOK_TILE * dn; e += blockDim.x) {
+        const int i = e / dn, d = e - i * dn;
+        qs[e] = i < nt ? q[((long long)(t0 + i) * H + h) * hd + d] : 0.f;
+    }
+    __syncthreads();
+    const TW* u = uk + (long long)h * dn * rank;
+    for (int r = tid; r < rank; r += blockDim.x) {
+        float acc[TOK_TILE];
+#pragma unroll
+        for (int i = 0; i < TOK_TILE; ++i) acc[i] = 0.f;
+        for (int d = 0; d < dn; ++d) {
+            const float w = lp_to_float(u[(long long)d * rank + r]);
+#pragma unroll
+            for (int i = 0; i < TOK_TILE; ++i) acc[i] = fmaf(qs[i * dn + d], w, acc[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < TOK_TILE; ++i)
+            if (i < nt) qa[((long long)(t0 + i) * H + h) * Dk + r] = acc[i];
+    }
+    for (int e = tid; e < nt * dr; e += blockDim.x) {
+        const int i = e / dr, d = e - i * dr;
+        qa[((long long)(t0 + i) * H + h) * Dk + rank + d] = q[((long long)(t0 + i) * H + h) * hd + dn + d];
+    }
+}
+
+// ---------------------------------------------------------------- attend
+// A CTA takes ROWS = WARPS * RW consecutive (token, head) rows of one sequence (heads of a token lie
+// together, so a warp's rows mostly share their causal limit) and one share of the sequence's key blocks.
+// Per block of 32 keys: the rows of the block go to shared memory as float32; lane j scores key j for the
+// warp's RW rows; maximum and sum are updated per row across the warp; then lane c owns columns c, c + 32,
+// ... of the latent sum and adds the 32 weighted rows in increasing key order.
+template <typename TKV, int RW, int NC>
+__global__ void __launch_bounds__(WARPS * 32)
+latent_attend_kernel(const float* __restrict__ qa, const TKV* __restrict__ pages, const int* __restrict__ page_table,
+                     int pt_stride, const int* __restrict__ q_start, const int* __restrict__ kv_len,
+                     float* __restrict__ part, int H, int rank, int dr, int page_size, float scale, int shares) {
+    extern __shared__ float smem[];
+    constexpr int ROWS = WARPS * RW;
+    const int Dk = rank + dr, KS = Dk + 1;
+    float* Qs = smem;                       // [ROWS][Dk]
+    float* Ks = smem + ROWS * Dk;           // [KEYS][Dk + 1]
+    lp_grid_release();
+    lp_grid_wait();
+    const int b = blockIdx.y, share = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int first_tok = q_start[b], n_new = q_start[b + 1] - first_tok;
+    const int len = kv_len[b];
+    const int rows_total = n_new * H;
+    const int r0 = blockIdx.x * ROWS;
+    if (r0 >= rows_total) return;
+    const int n_rows = min(ROWS, rows_total - r0);
+    const int first_pos = len - n_new;                    // position of the sequence's first new token
+    // queries of this CTA
+    for (int e = tid; e < ROWS * Dk; e += blockDim.x) {
+        const int r = e / Dk;
+        Qs[e] = r < n_rows ? qa[((long long)first_tok * H + r0) * Dk + e] : 0.f;
+    }
+    int pos_r[RW];
+    float m[RW], l[RW], o[RW][NC];
+#pragma unroll
+    for (int r = 0; r < RW; ++r) {
+        const int row = r0 + warp * RW + r;
+        pos_r[r] = row < rows_total ? first_pos + row / H : -1;
+        m[r] = -INFINITY;
+        l[r] = 0.f;
+#pragma unroll
+        for (int c = 0; c < NC; ++c) o[r][c] = 0.f;
+    }
+    const int last_pos = first_pos + (r0 + n_rows - 1) / H;          // the CTA's largest causal limit
+    const int blocks_seq = (len + KEYS - 1) / KEYS;
+    const int per = (blocks_seq + shares - 1) / shares;
+    const int blk_lo = share * per;
+    const int blk_hi = min(min((share + 1) * per, blocks_seq), last_pos / KEYS + 1);
+    const int* pt = page_table + (long long)b * pt_stride;
+    for (int blk = blk_lo; blk < blk_hi; ++blk) {
+        const int k0 = blk * KEYS;
+        __syncthreads();                                  // the previous block has been used (and Qs is written)
+        for (int j = warp; j < KEYS; j += WARPS) {
+            const int kp = k0 + j;
+            float* dst = Ks + j * KS;
+            if (kp <= last_pos) {
+                const TKV* src = pages + ((long long)pt[kp / page_size] * page_size + kp % page_size) * Dk;
+                for (int e = lane; e < Dk; e += 32) dst[e] = lp_to_float(src[e]);
+            } else {
+                for (int e = lane; e < Dk; e += 32) dst[e] = 0.f;
+            }
+        }
+        __syncthreads();
+        int warp_last = pos_r[0];
+#pragma unroll
+        for (int r = 1; r < RW; ++r) warp_last = max(warp_last, pos_r[r]);
+        if (warp_last < k0) continue;                                 // nothing of this block is visible to the warp
+        float dot[RW];
+#pragma unroll
+        for (int r = 0; r < RW; ++r) dot[r] = 0.f;
+        const float* kr = Ks + lane * KS;
+        const float* qw = Qs + warp * RW * Dk;
+        for (int d = 0; d < Dk; ++d) {
+            const float kv = kr[d];
+#pragma unroll
+            for (int r = 0; r < RW; ++r) dot[r] = fmaf(qw[r * Dk + d], kv, dot[r]);
+        }
+        float p[RW];
+#pragma unroll
+        for (int r = 0; r < RW; ++r) {
+            const bool seen = k0 + lane <= pos_r[r];
+            const float sc = seen ? dot[r] * scale : -INFINITY;
+            const float m_new = fmaxf(m[r], lp_warp_max(sc));
+            float alpha = 1.f;
+            p[r] = 0.f;
+            if (m_new != -INFINITY) {
+                p[r] = seen ? expf(sc - m_new) : 0.f;
+                alpha = (m[r] == -INFINITY) ? 0.f : expf(m[r] - m_new);
+            }
+            l[r] = l[r] * alpha + lp_warp_sum(p[r]);
+            m[r] = m_new;
+#pragma unroll
+            for (int c = 0; c < NC; ++c) o[r][c] *= alpha;
+        }
+        for (int j = 0; j < KEYS; ++j) {
+            float pj[RW];
+#pragma unroll
+            for (int r = 0; r < RW; ++r) pj[r] = __shfl_sync(0xffffffffu, p[r], j);
+            const float* cj = Ks + j * KS;
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                const int col = lane + 32 * c;
+                if (col < rank) {
+                    const float cv = cj[col];
+#pragma unroll
+                    for (int r = 0; r < RW; ++r) o[r][c] = fmaf(pj[r], cv, o[r][c]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < RW; ++r) {
+        const int row = r0 + warp * RW + r;
+        if (row >= rows_total) continue;
+        float* dst = part + (((long long)first_tok * H + row) * shares + share) * (rank + 2);
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+            const int col = lane + 32 * c;
+            if (col < rank) dst[col] = o[r][c];
+        }
+        if (lane == 0) {
+            dst[rank] = m[r];
+            dst[rank + 1] = l[r];
+        }
+    }
+}
+
+// ---------------------------------------------------------------- expand
+// out[t, h * dv + v] = gate(t, h) * sum_r W[h * dv + v, r] * latent[t, h, r], where latent is the merge of
+// the shares: sum_s o_s e^(m_s - M) / sum_s l_s e^(m_s - M). One warp per output feature, lanes over r.
+template <typename TW, typename TOut>
+__global__ void __launch_bounds__(128)
+latent_expand_kernel(const float* __restrict__ part, int shares, const TW* __restrict__ uv,
+                     const float* __restrict__ gate, int ldg, TOut* __restrict__ out, int T, int H, int rank, int dv) {
+    extern __shared__ float ls[];                         // [TOK_TILE][rank]
+    __shared__ float gs[TOK_TILE];
+    lp_grid_release();
+    lp_grid_wait();
+    const int t0 = blockIdx.x * TOK_TILE, h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nt = min(TOK_TILE, T - t0);
+    for (int i = 0; i < TOK_TILE; ++i) {
+        if (i >= nt) {
+            for (int r = tid; r < rank; r += blockDim.x) ls[i * rank + r] = 0.f;
+            continue;
+        }
+        const float* p = part + ((long long)(t0 + i) * H + h) * shares * (rank + 2);
+        float M = -INFINITY;
+        for (int s = 0; s < shares; ++s) M = fmaxf(M, p[s * (rank + 2) + rank]);
+        float L = 0.f;
+        for (int s = 0; s < shares; ++s) {
+            const float ms = p[s * (rank + 2) + rank];
+            if (ms != -INFINITY) L += p[s * (rank + 2) + rank + 1] * expf(ms - M);
+        }
+        const float inv = 1.0f / L;
+        for (int r = tid; r < rank; r += blockDim.x) {
+            float acc = 0.f;
+            for (int s = 0; s < shares; ++s) {
+                const float ms = p[s * (rank + 2) + rank];
+                if (ms != -INFINITY) acc = fmaf(p[s * (rank + 2) + r], expf(ms - M), acc);
+            }
+            ls[i * rank + r] = acc * inv;
+        }
+        if (tid == 0) gs[i] = gate ? 1.0f / (1.0f + expf(-gate[(long long)(t0 + i) * ldg + h])) : 1.0f;
+    }
+    __syncthreads();
+    for (int v = warp; v < dv; v += 4) {
+        const TW* w = uv + ((long long)h * dv + v) * rank;
+        float acc[TOK_TILE];
+#pragma unroll
+        for (int i = 0; i < TOK_TILE; ++i) acc[i] = 0.f;
+        for (int r = lane; r < rank; r += 32) {
+            const float wv = lp_to_float(w[r]);
+#pragma unroll
+            for (int i = 0; i < TOK_TILE; ++i) acc[i] = fmaf(ls[i * rank + r], wv, acc[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < TOK_TILE; ++i) {
+            const float s = lp_warp_sum(acc[i]);
+            if (lane == 0 && i < nt) out[((long long)(t0 + i) * H + h) * dv + v] = lp_from_float<TOut>(s * gs[i]);
+        }
+    }
+}
+
+template <typename K>
+int grant_shared(K kernel, size_t bytes, const char* what) {
+    if (bytes > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) {
+            snprintf(lp_error_text, sizeof(lp_error_text), "%s: cannot reserve %zu bytes of shared memory: %s", what, bytes,
+                     cudaGetErrorString(e));
+            return -1;
+        }
+    }
+    return 0;
+}
+
+}  // namespace
+
+// proj: float32 [T, ld] with the queries at q_off ([H, dn + dr]) and the latent and shared key part at kv_off
+// ([rank + dr]); pages: [num_pages, page_size, rank + dr]; q_out: float32 [T, H, dn + dr].
+extern "C" int lp_latent_prepare(const float* proj, int ld, int q_off, int kv_off, const float* gain, float eps,
+                                 const float* inv_freq, int rot, const int* positions, const int* seq_ids,
+                                 const int* page_table, int pt_stride, float* q_out, void* pages, int kv_dtype, int T,
+                                 int H, int dn, int dr, int rank, int page_size, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || dn < 0 || dr < 0 || rank <= 0 || dn + dr <= 0) LP_REFUSE("latent_prepare: %d heads of %d + %d over rank %d", H, dn, dr, rank);
+    if (rot < 0 || (rot & 1) || rot > dr || rot > 256) LP_REFUSE("latent_prepare: rotary width %d of %d (even, at most 256)", rot, dr);
+    if (rot > 0 && !inv_freq) LP_REFUSE("latent_prepare: rotation without frequencies");
+    if (page_size <= 0) LP_REFUSE("latent_prepare: page size %d", page_size);
+    if (q_off < 0 || kv_off < 0 || q_off + H * (dn + dr) > ld || kv_off + rank + dr > ld)
+        LP_REFUSE("latent_prepare: slices at %d and %d do not fit rows of %d", q_off, kv_off, ld);
+#define LP_LAUNCH_PREP(TKV)                                                                                       \
+    lp_launch(latent_prepare_kernel<TKV>, T, 256, 0, stream, proj, ld, q_off, kv_off, gain, eps, inv_freq, rot,    \
+              positions, seq_ids, page_table, pt_stride, q_out, (TKV*)pages, H, dn, dr, rank, page_size)
+    if (kv_dtype == LP_F32) LP_LAUNCH_PREP(float);
+    else if (kv_dtype == LP_BF16) LP_LAUNCH_PREP(__nv_bfloat16);
+    else LP_REFUSE("latent_prepare: cache dtype code %d", kv_dtype);
+#undef LP_LAUNCH_PREP
+    return lp_check_launch("latent_prepare");
+}
+
+// q: float32 [T, H, dn + dr]; uk: [H * dn, rank]; qa: float32 [T, H, rank + dr].
+extern "C" int lp_latent_absorb(const float* q, const void* uk, int w_dtype, float* qa, int T, int H, int dn, int dr,
+                                int rank, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || H > 65535 || dn < 0 || dr < 0 || rank <= 0) LP_REFUSE("latent_absorb: %d heads of %d + %d over rank %d", H, dn, dr, rank);
+    dim3 grid((T + TOK_TILE - 1) / TOK_TILE, H);
+    const size_t smem = (size_t)TOK_TILE * (dn > 0 ? dn : 1) * sizeof(float);
+    if (w_dtype == LP_F32) {
+        if (grant_shared(latent_absorb_kernel<float>, smem, "latent_absorb")) return -1;
+        lp_launch(latent_absorb_kernel<float>, grid, 128, smem, stream, q, (const float*)uk, qa, T, H, dn, dr, rank);
+    } else if (w_dtype == LP_BF16) {
+        if (grant_shared(latent_absorb_kernel<__nv_bfloat16>, smem, "latent_absorb")) return -1;
+        lp_launch(latent_absorb_kernel<__nv_bfloat16>, grid, 128, smem, stream, q, (const __nv_bfloat16*)uk, qa, T, H, dn, dr, rank);
+    } else LP_REFUSE("latent_absorb: weight dtype code %d", w_dtype);
+    return lp_check_launch("latent_absorb");
+}
+
+constexpr int ATTEND_RW = 4;
+
+// How many (token, head) rows one CTA of lp_latent_attend takes.
+extern "C" int lp_latent_attend_rows() { return WARPS * ATTEND_RW; }
+
+// qa: float32 [T, H, rank + dr]; part: float32 [T, H, shares, rank + 2] (unnormalised sums, maximum, sum of
+// weights); q_start [B + 1], kv_len [B] (lengths after the step); max_new: most new tokens of a sequence.
+extern "C" int lp_latent_attend(const float* qa, const void* pages, int kv_dtype, const int* page_table, int pt_stride,
+                                const int* q_start, const int* kv_len, float* part, int B, int max_new, int H,
+                                int rank, int dr, int page_size, float scale, int shares, cudaStream_t stream) {
+    if (B <= 0 || max_new <= 0) return 0;
+    if (H <= 0 || rank <= 0 || dr < 0) LP_REFUSE("latent_attend: %d heads over rank %d + %d", H, rank, dr);
+    if (rank > 512) LP_REFUSE("latent_attend: rank %d (supported: up to 512)", rank);
+    if (page_size <= 0 || page_size % KEYS) LP_REFUSE("latent_attend: page size %d must be a multiple of %d", page_size, KEYS);
+    if (shares <= 0 || shares > 65535 || B > 65535) LP_REFUSE("latent_attend: %d shares, %d sequences", shares, B);
+    constexpr int ROWS = WARPS * ATTEND_RW;
+    const int Dk = rank + dr;
+    const size_t smem = ((size_t)ROWS * Dk + (size_t)KEYS * (Dk + 1)) * sizeof(float);
+    if (smem > 227 * 1024) LP_REFUSE("latent_attend: rows of %d values need %zu bytes of shared memory", Dk, smem);
+    dim3 grid((unsigned)(((long long)max_new * H + ROWS - 1) / ROWS), B, shares);
+#define LP_LAUNCH_ATTEND(TKV, NC)                                                                                    \
+    do {                                                                                                             \
+        if (grant_shared(latent_attend_kernel<TKV, ATTEND_RW, NC>, smem, "latent_attend")) return -1;                \
+        lp_launch(latent_attend_kernel<TKV, ATTEND_RW, NC>, grid, WARPS * 32, smem, stream, qa, (const TKV*)pages,   \
+                  page_table, pt_stride, q_start, kv_len, part, H, rank, dr, page_size, scale, shares);              \
+    } while (0)
+#define LP_PICK_NC(TKV)                                  \
+    do {                                                 \
+        if (rank <= 32) LP_LAUNCH_ATTEND(TKV, 1);        \
+        else if (rank <= 64) LP_LAUNCH_ATTEND(TKV, 2);   \
+        else if (rank <= 128) LP_LAUNCH_ATTEND(TKV, 4);  \
+        else if (rank <= 256) LP_LAUNCH_ATTEND(TKV, 8);  \
+        else LP_LAUNCH_ATTEND(TKV, 16);                  \
+    } while (0)
+    if (kv_dtype == LP_F32) LP_PICK_NC(float);
+    else if (kv_dtype == LP_BF16) LP_PICK_NC(__nv_bfloat16);
+    else LP_REFUSE("latent_attend: cache dtype code %d", kv_dtype);
+#undef LP_PICK_NC
+#undef LP_LAUNCH_ATTEND
+    return lp_check_launch("latent_attend");
+}
+
+// part: as lp_latent_attend leaves it; uv: [H * dv, rank]; gate: float32 [T, ldg] with one value per head
+// (or null); out: [T, H * dv].
+extern "C" int lp_latent_expand(const float* part, int shares, const void* uv, int w_dtype, const float* gate, int ldg,
+                                void* out, int out_dtype, int T, int H, int rank, int dv, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || H > 65535 || rank <= 0 || dv <= 0 || shares <= 0) LP_REFUSE("latent_expand: %d heads, rank %d, values of %d, %d shares", H, rank, dv, shares);
+    dim3 grid((T + TOK_TILE - 1) / TOK_TILE, H);
+    const size_t smem = (size_t)TOK_TILE * rank * sizeof(float);
+#define LP_LAUNCH_EXPAND(TW, TOut)                                                                                \
+    do {                                                                                                          \
+        if (grant_shared(latent_expand_kernel<TW, TOut>, smem, "latent_expand")) return -1;                       \
+        lp_launch(latent_expand_kernel<TW, TOut>, grid, 128, smem, stream, part, shares, (const TW*)uv, gate, ldg, \
+                  (TOut*)out, T, H, rank, dv);                                                                    \
+    } while (0)
+    if (w_dtype == LP_F32 && out_dtype == LP_F32) LP_LAUNCH_EXPAND(float, float);
+    else if (w_dtype == LP_BF16 && out_dtype == LP_BF16) LP_LAUNCH_EXPAND(__nv_bfloat16, __nv_bfloat16);
+    else if (w_dtype == LP_BF16 && out_dtype == LP_F32) LP_LAUNCH_EXPAND(__nv_bfloat16, float);
+    else if (w_dtype == LP_F32 && out_dtype == LP_BF16) LP_LAUNCH_EXPAND(float, __nv_bfloat16);
+    else LP_REFUSE("latent_expand: dtype codes w=%d out=%d", w_dtype, out_dtype);
+#undef LP_LAUNCH_EXPAND
+    return lp_check_launch("latent_expand");
+}

@@ -1,0 +1,202 @@
+// Gated linear attention: a matrix-valued recurrent state per head with a decay per key channel.
+//
+//     S_t = diag(a_t) S_(t-1) + k_t v_t^T        (S: [dk, dv], rows belong to key channels)
+//     o_t = S_t^T q_t
+//
+// with a_t = sigmoid(z_t)^(1/tau) and z_t = A2 (A1 h_t) + bias (a low-rank map of the layer's input).
+// The state is float32, one block [H, dk, dv] per sequence, read at the start of a step and written
+// back at its end; decays, their logarithms and every sum are float32.
+//
+//   lp_gla_decay    a[t, c] = exp(-softplus(-z[t, c]) / tau), z from the low-rank factor's output
+//   lp_gla_scan     the recurrence over a step's tokens, sequence by sequence, in token order
+//   lp_gla_finish   per head: RMS norm over dv (gain shared by heads), times silu(gate)
+#include "common.cuh"
+
+namespace {
+
+// ---------------------------------------------------------------- decay
+// low: float32 [T, ldl] slice with the R values A1 h; a2: [C, R]; bias: [C]; out: float32 [T, C].
+template <typename TW>
+__global__ void __launch_bounds__(256)
+gla_decay_kernel(const float* __restrict__ low, int ldl, const TW* __restrict__ a2, const float* __restrict__ bias,
+                 float* __restrict__ out, int T, int C, int R, float inv_tau) {
+    lp_grid_release();
+    lp_grid_wait();
+    const long long n = (long long)T * C;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / C;
+        const int c = (int)(i - t * C);
+        const float* x = low + t * ldl;
+        const TW* w = a2 + (long long)c * R;
+        float z = 0.f;
+        for (int r = 0; r < R; ++r) z = fmaf(lp_to_float(w[r]), x[r], z);
+        z += bias ? bias[c] : 0.f;
+        // log sigmoid(z) = -softplus(-z)
+        const float sp = fmaxf(-z, 0.f) + log1pf(expf(-fabsf(z)));
+        out[i] = expf(-sp * inv_tau);
+    }
+}
+
+// ---------------------------------------------------------------- scan
+// One CTA per (block of VT value columns, head, sequence); thread (j, part) keeps the state rows
+// part, part + KP, part + 2 KP, ... of value column j in registers. Tokens are brought to shared memory
+// TB at a time; per token every thread decays and updates its rows, forms its share of o_t[j], and the KP
+// shares meet in two shuffles.
+constexpr int KP = 4;             // threads that share a value column
+constexpr int VT = 64;            // value columns per CTA
+constexpr int TB = 16;            // tokens per round of loads
+
+template <int KPT>
+__global__ void __launch_bounds__(VT * KP)
+gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off, const float* __restrict__ decay,
+                float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ q_start,
+                float* __restrict__ out, int H, int dk, int dv, float q_scale) {
+    extern __shared__ float sm[];
+    float* qs = sm;                         // [TB][dk]
+    float* ks = qs + TB * dk;
+    float* as = ks + TB * dk;
+    float* vs = as + TB * dk;               // [TB][VT]
+    lp_grid_release();
+    lp_grid_wait();
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int tid = threadIdx.x, part = tid & (KP - 1), jl = tid >> 2;
+    const int j = blockIdx.x * VT + jl;
+    const bool live = j < dv;
+    const int t0 = q_start[b], t1 = q_start[b + 1];
+    float* S = state + ((long long)slots[b] * H + h) * dk * dv;
+    float s[KPT];
+#pragma unroll
+    for (int i = 0; i < KPT; ++i) {
+        const int c = part + KP * i;
+        s[i] = (live && c < dk) ? S[(long long)c * dv + j] : 0.f;
+    }
+    for (int tb = t0; tb < t1; tb += TB) {
+        const int nt = min(TB, t1 - tb);
+        __syncthreads();
+        for (int e = tid; e < nt * dk; e += blockDim.x) {
+            const int i = e / dk, c = e - i * dk;
+            const float* row = proj + (long long)(tb + i) * ld;
+            qs[e] = row[q_off + h * dk + c] * q_scale;
+            ks[e] = row[k_off + h * dk + c];
+            as[e] = decay[((long long)(tb + i) * H + h) * dk + c];
+        }
+        for (int e = tid; e < nt * VT; e += blockDim.x) {
+            const int i = e / VT, c = e - i * VT;
+            const int col = blockIdx.x * VT + c;
+            vs[e] = col < dv ? proj[(long long)(tb + i) * ld + v_off + h * dv + col] : 0.f;
+        }
+        __syncthreads();
+        for (int i = 0; i < nt; ++i) {
+            const float v = vs[i * VT + jl];
+            const float* qi = qs + i * dk;
+            const float* ki = ks + i * dk;
+            const float* ai = as + i * dk;
+            float acc = 0.f;
+#pragma unroll
+            for (int u = 0; u < KPT; ++u) {
+                const int c = part + KP * u;
+                if (c < dk) {
+                    s[u] = fmaf(ai[c], s[u], ki[c] * v);
+                    acc = fmaf(s[u], qi[c], acc);
+                }
+            }
+            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            if (part == 0 && live) out[((long long)(tb + i) * H + h) * dv + j] = acc;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < KPT; ++i) {
+        const int c = part + KP * i;
+        if (live && c < dk) S[(long long)c * dv + j] = s[i];
+    }
+}
+
+// ---------------------------------------------------------------- finish
+// out[t, h * dv + j] = o[t, h, j] / sqrt(mean_j o^2 + eps) * gain[j] * silu(gate[t, h * dv + j]); a warp per (t, h).
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+gla_finish_kernel(const float* __restrict__ o, const float* __restrict__ gain, float eps, const float* __restrict__ gate,
+                  int ldg, TOut* __restrict__ out, int T, int H, int dv) {
+    lp_grid_release();
+    lp_grid_wait();
+    const int lane = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= (long long)T * H) return;
+    const long long t = row / H;
+    const int h = (int)(row - t * H);
+    const float* x = o + row * dv;
+    float ss = 0.f;
+    for (int j = lane; j < dv; j += 32) ss += x[j] * x[j];
+    ss = lp_warp_sum(ss);
+    const float factor = 1.0f / sqrtf(ss / (float)dv + eps);
+    const float* g = gate ? gate + t * ldg + (long long)h * dv : nullptr;
+    for (int j = lane; j < dv; j += 32) {
+        float v = x[j] * factor * gain[j];
+        if (g) v *= g[j] / (1.0f + expf(-g[j]));
+        out[row * dv + j] = lp_from_float<TOut>(v);
+    }
+}
+
+}  // namespace
+
+extern "C" int lp_gla_decay(const float* low, int ldl, const void* a2, int w_dtype, const float* bias, float* out,
+                            int T, int C, int R, float tau, cudaStream_t stream) {
+    if (T <= 0 || C <= 0) return 0;
+    if (R <= 0 || ldl < R) LP_REFUSE("gla_decay: a factor of %d values in rows of %d", R, ldl);
+    if (!(tau > 0.f)) LP_REFUSE("gla_decay: temperature %g", (double)tau);
+    const long long n = (long long)T * C;
+    long long blocks = (n + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (w_dtype == LP_F32)
+        lp_launch(gla_decay_kernel<float>, (unsigned)blocks, 256, 0, stream, low, ldl, (const float*)a2, bias, out, T, C, R, 1.0f / tau);
+    else if (w_dtype == LP_BF16)
+        lp_launch(gla_decay_kernel<__nv_bfloat16>, (unsigned)blocks, 256, 0, stream, low, ldl, (const __nv_bfloat16*)a2, bias, out, T, C, R, 1.0f / tau);
+    else LP_REFUSE("gla_decay: weight dtype code %d", w_dtype);
+    return lp_check_launch("gla_decay");
+}
+
+// proj: float32 [T, ld] with queries at q_off ([H, dk]), keys at k_off ([H, dk]), values at v_off ([H, dv]);
+// decay: float32 [T, H * dk]; state: float32 [slots, H, dk, dv]; out: float32 [T, H, dv].
+extern "C" int lp_gla_scan(const float* proj, int ld, int q_off, int k_off, int v_off, const float* decay, float* state,
+                           const int* slots, const int* q_start, float* out, int B, int H, int dk, int dv,
+                           float q_scale, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (H <= 0 || H > 65535 || B > 65535 || dk <= 0 || dv <= 0) LP_REFUSE("gla_scan: %d sequences, %d heads of %d x %d", B, H, dk, dv);
+    if (dk > 512) LP_REFUSE("gla_scan: %d key channels per head (supported: up to 512)", dk);
+    if (q_off < 0 || k_off < 0 || v_off < 0 || q_off + H * dk > ld || k_off + H * dk > ld || v_off + H * dv > ld)
+        LP_REFUSE("gla_scan: slices at %d, %d, %d do not fit rows of %d", q_off, k_off, v_off, ld);
+    dim3 grid((dv + VT - 1) / VT, H, B);
+    const size_t smem = ((size_t)3 * TB * dk + (size_t)TB * VT) * sizeof(float);
+    const int kpt = (dk + KP - 1) / KP;
+#define LP_LAUNCH_SCAN(N)                                                                                             \
+    lp_launch(gla_scan_kernel<N>, grid, VT * KP, smem, stream, proj, ld, q_off, k_off, v_off, decay, state, slots,     \
+              q_start, out, H, dk, dv, q_scale)
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaSuccess;
+        if (kpt <= 64) e = cudaFuncSetAttribute(gla_scan_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        else e = cudaFuncSetAttribute(gla_scan_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) LP_REFUSE("gla_scan: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    }
+    if (kpt <= 4) LP_LAUNCH_SCAN(4);
+    else if (kpt <= 8) LP_LAUNCH_SCAN(8);
+    else if (kpt <= 16) LP_LAUNCH_SCAN(16);
+    else if (kpt <= 32) LP_LAUNCH_SCAN(32);
+    else if (kpt <= 64) LP_LAUNCH_SCAN(64);
+    else LP_LAUNCH_SCAN(128);
+#undef LP_LAUNCH_SCAN
+    return lp_check_launch("gla_scan");
+}
+
+extern "C" int lp_gla_finish(const float* o, const float* gain, float eps, const float* gate, int ldg, void* out,
+                             int out_dtype, int T, int H, int dv, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || dv <= 0) LP_REFUSE("gla_finish: %d heads of %d", H, dv);
+    const long long rows = (long long)T * H;
+    const unsigned blocks = (unsigned)((rows + 7) / 8);
+    if (out_dtype == LP_F32) lp_launch(gla_finish_kernel<float>, blocks, 256, 0, stream, o, gain, eps, gate, ldg, (float*)out, T, H, dv);
+    else if (out_dtype == LP_BF16)
+        lp_launch(gla_finish_kernel<__nv_bfloat16>, blocks, 256, 0, stream, o, gain, eps, gate, ldg, (__nv_bfloat16*)out, T, H, dv);
+    else LP_REFUSE("gla_finish: output dtype code %d", out_dtype);
+    return lp_check_launch("gla_finish");
+}

@@ -53,6 +53,9 @@ class Engine:
         self._fused = {}               # captured decode steps with upload, argmax and read-back inside
         self._last_ctx: Optional[StepContext] = None
         self._prepared = None          # (context, page tables): the next decode step's pages, reserved ahead
+        from ..cache.sequence_cache import StateRequest
+        # whether a run keeps a state that a step changes in place (running a step twice would change it twice)
+        self._keeps_state = any(isinstance(r, StateRequest) for r in model.cache_requests())
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -375,6 +378,12 @@ class Engine:
                            d["prob"], select=d["select"])
             landing[:B].copy_(sampled, non_blocking=True)
 
+        if entry is None and draw is not None and self._keeps_state:
+            # a recurrent state must not see a step twice, so nothing runs "for nothing" here: this step goes the
+            # plain way (which sizes the model's buffers; the sampler's were sized above), later ones are captured
+            self._fused[key] = {"graph": None, "version": self.workspace.version}
+            self._last_ctx = None
+            return None
         try:
             if entry is None and draw is not None:
                 # a shape's first step with a sampler: run once for nothing (it sizes every buffer; the step's keys

@@ -34,6 +34,8 @@ LIBRARIES: Dict[str, str] = {
     "attention_mma": "attention_mma.cu",
     "attention_tcgen05": "attention_tcgen05.cu",
     "host_loop": "host_loop.cu",
+    "latent_attention": "latent_attention.cu",
+    "linear_attention": "linear_attention.cu",
 }
 HEADERS = ("common.cuh", "attention_noalloc.h", "tcgen05_utils.cuh", "attention_decode.cuh")
 

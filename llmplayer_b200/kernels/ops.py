@@ -23,7 +23,10 @@ _CODES = {torch.float32: F32, torch.bfloat16: BF16}
 _P, _I, _F = c_void_p, c_int, c_float
 _SIGNATURES = {
     "elementwise": {
-        "lp_embed": [_P, _I, _P, _P, _I, _I, _P],
+        "lp_embed": [_P, _I, _P, _P, _I, _I, _F, _P],
+        "lp_layernorm": [_P, _P, _P, _P, _I, _I, _I, _F, _P],
+        "lp_xielu": [_P, _I, _P, _P, _I, _I, _I, _P],
+        "lp_gated_sum": [_P, _P, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P],
         "lp_rmsnorm": [_P, _P, _I, _P, _P, _P, _I, _I, _I, _F, _P, ctypes.c_longlong, _P],
         "lp_rope_cache_write": [_P, _I, _P, _P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
         "lp_advance": [_P, _P, _P, _P, _I, _P],
@@ -53,6 +56,18 @@ _SIGNATURES = {
     "attention_tcgen05": {
         "lp_attention_prefill_tc": [_P, _P, _P, ctypes.c_longlong, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I,
                                     _P, _P],
+    },
+    "latent_attention": {
+        "lp_latent_prepare": [_P, _I, _I, _I, _P, _F, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+        "lp_latent_absorb": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _P],
+        "lp_latent_attend_rows": [],
+        "lp_latent_attend": [_P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+        "lp_latent_expand": [_P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P],
+    },
+    "linear_attention": {
+        "lp_gla_decay": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _F, _P],
+        "lp_gla_scan": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _P],
+        "lp_gla_finish": [_P, _P, _F, _P, _I, _P, _I, _I, _I, _I, _P],
     },
     "host_loop": {
         "lp_decode_loop": [_P, _P, _P, _I, _I, _I, _P, _I, _I, _P, _P, _P, _P, _P],
@@ -311,8 +326,8 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
 
 
 # --------------------------------------------------------------------------- embedding
-def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t, :] = float32(table[tokens[t], :])."""
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """out[t, :] = float32(table[tokens[t], :]) * scale."""
     _want(table, "embed table", ndim=2)
     _want(tokens, "embed tokens", torch.int32, 1)
     _want(out, "embed out", torch.float32, 2)
@@ -321,7 +336,7 @@ def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> torch
         raise KernelError(f"embed: {tokens.numel()} tokens, table {tuple(table.shape)}, out {tuple(out.shape)}")
     lib = library("elementwise")
     _check(lib, lib.lp_embed(table.data_ptr(), _code(table, "embed table"), tokens.data_ptr(), out.data_ptr(),
-                             T, d, _stream()))
+                             T, d, float(scale), _stream()))
     return out
 
 
@@ -361,6 +376,92 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
                                _code(out, "rmsnorm out"), R, d, float(eps), _ptr(clear),
                                clear.numel() if clear is not None else 0, _stream()))
     return out
+
+
+def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+              rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[r] = (x[rows[r]] - mean) / sqrt(variance + eps) * weight, float32 inside; the variance is the mean
+    of the squared deviations from the mean."""
+    _want(x, "layernorm x", torch.float32, 2)
+    _want(weight, "layernorm weight", torch.float32, 1)
+    _want(out, "layernorm out", ndim=2)
+    d, R = x.shape[1], out.shape[0]
+    if weight.numel() != d or out.shape[1] != d:
+        raise KernelError(f"layernorm: x {tuple(x.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+    if rows is not None:
+        _want(rows, "layernorm rows", torch.int32, 1)
+        if rows.numel() != R:
+            raise KernelError(f"layernorm: {rows.numel()} row indices for {R} output rows")
+    elif x.shape[0] != R:
+        raise KernelError(f"layernorm: x {tuple(x.shape)} and out {tuple(out.shape)} differ in rows")
+    lib = library("elementwise")
+    _check(lib, lib.lp_layernorm(x.data_ptr(), _ptr(rows), weight.data_ptr(), out.data_ptr(), _code(out, "layernorm out"),
+                                 R, d, float(eps), _stream()))
+    return out
+
+
+def _slice(t: torch.Tensor, what: str):
+    """(pointer, row stride) of a float32 matrix that may be a column slice of a wider one."""
+    if not isinstance(t, torch.Tensor) or not t.is_cuda or t.dtype != torch.float32 or t.dim() != 2:
+        raise KernelError(f"{what}: expected a float32 CUDA matrix")
+    if t.stride(1) != 1 and t.shape[1] > 1:
+        raise KernelError(f"{what}: columns must lie together, got strides {t.stride()}")
+    return t.data_ptr(), int(t.stride(0))
+
+
+def xielu(z: torch.Tensor, pq: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out = softplus(p) z^2 + z / 2 where z > 0, (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2 elsewhere;
+    ``z``: float32 [T, F] (may be a column slice), ``pq``: float32 [2] on the device."""
+    zp, ldz = _slice(z, "xielu z")
+    _want(pq, "xielu numbers", torch.float32, 1)
+    _want(out, "xielu out", ndim=2)
+    if out.shape != z.shape or pq.numel() != 2:
+        raise KernelError(f"xielu: z {tuple(z.shape)}, out {tuple(out.shape)}, {pq.numel()} numbers")
+    lib = library("elementwise")
+    _check(lib, lib.lp_xielu(zp, ldz, pq.data_ptr(), out.data_ptr(), _code(out, "xielu out"), z.shape[0], z.shape[1],
+                             _stream()))
+    return out
+
+
+def gated_sum(x: torch.Tensor, a: Optional[torch.Tensor], a_gate=None, b: Optional[torch.Tensor] = None, b_gate=None, *,
+              streams: Optional[torch.Tensor] = None, mix: Optional[torch.Tensor] = None, count: int = 0,
+              keep_input: bool = False) -> torch.Tensor:
+    """x <- x + a * sigmoid(ga + ba) + b * sigmoid(gb + bb), float32, in place. ``a_gate`` / ``b_gate``:
+    ``(logits [T, d], may be a column slice; bias [d] or None)`` or None for an ungated branch; ``b`` may be None.
+    ``streams`` [>= count, T, d] with ``mix`` [count]: the sum is kept as stream ``count - 1`` and x becomes
+    sum_j mix[j] * streams[j]; ``keep_input`` first stores the incoming x as stream ``count - 2``."""
+    _want(x, "gated_sum x", torch.float32, 2)
+    T, d = x.shape
+
+    def branch(t, gate, what):
+        if t is None:
+            return None, None, 0, None
+        _want(t, f"gated_sum {what}", torch.float32, 2)
+        if t.shape != x.shape:
+            raise KernelError(f"gated_sum: {what} {tuple(t.shape)} does not match x {tuple(x.shape)}")
+        if gate is None:
+            return t.data_ptr(), None, 0, None
+        logits, bias = gate
+        gp, ldg = _slice(logits, f"gated_sum {what} gate")
+        if logits.shape != x.shape:
+            raise KernelError(f"gated_sum: {what} gate {tuple(logits.shape)} does not match x {tuple(x.shape)}")
+        if bias is not None:
+            _want(bias, f"gated_sum {what} gate bias", torch.float32, 1)
+            if bias.numel() != d:
+                raise KernelError(f"gated_sum: a gate bias of {bias.numel()} values for rows of {d}")
+        return t.data_ptr(), gp, ldg, _ptr(bias)
+
+    ap, agp, ald, abp = branch(a, a_gate, "a")
+    bp, bgp, bld, bbp = branch(b, b_gate, "b")
+    if streams is not None:
+        _want(streams, "gated_sum streams", torch.float32, 3)
+        _want(mix, "gated_sum mix", torch.float32, 1)
+        if streams.shape[1:] != x.shape or streams.shape[0] < count or mix.numel() != count or count < 1:
+            raise KernelError(f"gated_sum: streams {tuple(streams.shape)}, {mix.numel()} weights, count {count}")
+    lib = library("elementwise")
+    _check(lib, lib.lp_gated_sum(x.data_ptr(), ap, agp, ald, abp, bp, bgp, bld, bbp, _ptr(streams), _ptr(mix), int(count),
+                                 1 if keep_input else 0, T, d, _stream()))
+    return x
 
 
 # --------------------------------------------------------------------------- rotation + cache write
@@ -892,6 +993,177 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, page
                                  window=window)
     return attention_plain(q, out, pages, page_table, ctx.seq_ids, ctx.positions, num_heads=num_heads,
                            num_kv_heads=num_kv_heads, head_dim=head_dim, scale=scale, window=window)
+
+
+# --------------------------------------------------------------------------- latent attention
+def latent_prepare(proj: torch.Tensor, q_off: int, kv_off: int, gain: torch.Tensor, eps: float, rotation: Rotation,
+                   positions: torch.Tensor, seq_ids: torch.Tensor, page_table: torch.Tensor, q_out: torch.Tensor,
+                   pages: torch.Tensor, *, num_heads: int, nope_dim: int, rope_dim: int, kv_rank: int) -> None:
+    """From the float32 projection ``proj`` [T, F] (queries at column ``q_off``, [H, nope + rope]; latent and
+    shared key part at ``kv_off``, [rank + rope]): RMS-norm the latent with ``gain``, rotate the shared key
+    part and write both into ``pages`` [num_pages, page_size, rank + rope] at the tokens' positions; rotate the
+    queries' rope parts and write the queries to ``q_out`` float32 [T, H, nope + rope]."""
+    _want(proj, "latent_prepare proj", torch.float32, 2)
+    _want(gain, "latent_prepare gain", torch.float32, 1)
+    _want(positions, "latent_prepare positions", torch.int32, 1)
+    _want(seq_ids, "latent_prepare seq_ids", torch.int32, 1)
+    _want(page_table, "latent_prepare page_table", torch.int32, 2)
+    _want(q_out, "latent_prepare q_out", torch.float32, 3)
+    _want(pages, "latent_prepare pages", ndim=3)
+    T = proj.shape[0]
+    H, dn, dr, rank = num_heads, nope_dim, rope_dim, kv_rank
+    if (q_out.shape != (T, H, dn + dr) or pages.shape[2] != rank + dr or gain.numel() != rank
+            or positions.numel() != T or seq_ids.numel() != T):
+        raise KernelError(f"latent_prepare: proj {tuple(proj.shape)}, q_out {tuple(q_out.shape)}, pages "
+                          f"{tuple(pages.shape)} for {H} heads of {dn} + {dr} over rank {rank}")
+    freq_ptr, rot, interleaved = rotation.checked("latent_prepare")
+    if interleaved:
+        raise KernelError("latent_prepare: pairs of neighbours are not supported, only (i, i + half)")
+    lib = library("latent_attention")
+    _check(lib, lib.lp_latent_prepare(
+        proj.data_ptr(), proj.shape[1], int(q_off), int(kv_off), gain.data_ptr(), float(eps), freq_ptr, rot,
+        positions.data_ptr(), seq_ids.data_ptr(), page_table.data_ptr(), page_table.shape[1], q_out.data_ptr(),
+        pages.data_ptr(), _code(pages, "latent_prepare pages"), T, H, dn, dr, rank, pages.shape[1], _stream()))
+
+
+def latent_absorb(q: torch.Tensor, k_up: torch.Tensor, out: torch.Tensor, *, nope_dim: int, rope_dim: int) -> torch.Tensor:
+    """out[t, h] = [k_up[h]^T q[t, h, :nope] | q[t, h, nope:]]: float32 [T, H, rank + rope] from ``q`` float32
+    [T, H, nope + rope] and ``k_up`` [H * nope, rank]."""
+    _want(q, "latent_absorb q", torch.float32, 3)
+    _want(k_up, "latent_absorb k_up", ndim=2)
+    _want(out, "latent_absorb out", torch.float32, 3)
+    T, H, hd = q.shape
+    rank = k_up.shape[1]
+    if hd != nope_dim + rope_dim or k_up.shape[0] != H * nope_dim or out.shape != (T, H, rank + rope_dim):
+        raise KernelError(f"latent_absorb: q {tuple(q.shape)}, k_up {tuple(k_up.shape)}, out {tuple(out.shape)}")
+    lib = library("latent_attention")
+    _check(lib, lib.lp_latent_absorb(q.data_ptr(), k_up.data_ptr(), _code(k_up, "latent_absorb k_up"), out.data_ptr(),
+                                     T, H, nope_dim, rope_dim, rank, _stream()))
+    return out
+
+
+def latent_shares(batch: int, max_new: int, num_heads: int, table_width: int, page_size: int) -> int:
+    """Into how many shares :func:`latent_attend` cuts a sequence's keys: one while the (token, head) rows
+    alone fill the SMs, else as many as leave each share at least four pages."""
+    rows = library("latent_attention").lp_latent_attend_rows()
+    ctas = batch * -(-max_new * num_heads // rows)
+    return max(1, min(num_sms() // max(ctas, 1), table_width // 4))
+
+
+def latent_attend(q_abs: torch.Tensor, pages: torch.Tensor, page_table: torch.Tensor, q_start: torch.Tensor,
+                  kv_len: torch.Tensor, partials: torch.Tensor, *, max_new: int, kv_rank: int, scale: float) -> torch.Tensor:
+    """Causal softmax attention of the absorbed queries ``q_abs`` float32 [T, H, rank + rope] over the rows of
+    ``pages`` [num_pages, page_size, rank + rope]; ``partials`` float32 [T, H, shares, rank + 2] receives each
+    share's unnormalised latent sum, maximum and sum of weights."""
+    _want(q_abs, "latent_attend q", torch.float32, 3)
+    _want(pages, "latent_attend pages", ndim=3)
+    _want(page_table, "latent_attend page_table", torch.int32, 2)
+    _want(q_start, "latent_attend q_start", torch.int32, 1)
+    _want(kv_len, "latent_attend kv_len", torch.int32, 1)
+    _want(partials, "latent_attend partials", torch.float32, 4)
+    T, H, Dk = q_abs.shape
+    B = kv_len.numel()
+    shares = partials.shape[2]
+    if (pages.shape[2] != Dk or kv_rank > Dk or partials.shape != (T, H, shares, kv_rank + 2)
+            or q_start.numel() != B + 1 or page_table.shape[0] != B):
+        raise KernelError(f"latent_attend: q {tuple(q_abs.shape)}, pages {tuple(pages.shape)}, partials "
+                          f"{tuple(partials.shape)}, {B} sequences")
+    lib = library("latent_attention")
+    _check(lib, lib.lp_latent_attend(q_abs.data_ptr(), pages.data_ptr(), _code(pages, "latent_attend pages"),
+                                     page_table.data_ptr(), page_table.shape[1], q_start.data_ptr(), kv_len.data_ptr(),
+                                     partials.data_ptr(), B, int(max_new), H, kv_rank, Dk - kv_rank, pages.shape[1],
+                                     float(scale), shares, _stream()))
+    return partials
+
+
+def latent_expand(partials: torch.Tensor, v_up: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, *,
+                  value_dim: int) -> torch.Tensor:
+    """out[t, h * dv + v] = sigmoid(gate[t, h]) * (v_up[h] latent[t, h])[v], the latent being the merge of the
+    shares in ``partials``; ``gate``: float32 [T, H] (may be a column slice) or None."""
+    _want(partials, "latent_expand partials", torch.float32, 4)
+    _want(v_up, "latent_expand v_up", ndim=2)
+    _want(out, "latent_expand out", ndim=2)
+    T, H, shares, width = partials.shape
+    rank = width - 2
+    if v_up.shape != (H * value_dim, rank) or out.shape != (T, H * value_dim):
+        raise KernelError(f"latent_expand: partials {tuple(partials.shape)}, v_up {tuple(v_up.shape)}, out {tuple(out.shape)}")
+    gp, ldg = (None, 0)
+    if gate is not None:
+        gp, ldg = _slice(gate, "latent_expand gate")
+        if gate.shape != (T, H):
+            raise KernelError(f"latent_expand: gate {tuple(gate.shape)} for {T} tokens and {H} heads")
+    lib = library("latent_attention")
+    _check(lib, lib.lp_latent_expand(partials.data_ptr(), shares, v_up.data_ptr(), _code(v_up, "latent_expand v_up"), gp, ldg,
+                                     out.data_ptr(), _code(out, "latent_expand out"), T, H, rank, value_dim, _stream()))
+    return out
+
+
+# --------------------------------------------------------------------------- gated linear attention
+def gla_decay(low: torch.Tensor, up: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, tau: float) -> torch.Tensor:
+    """out[t, c] = sigmoid(up[c] . low[t] + bias[c]) ** (1 / tau), float32; ``low``: float32 [T, R] (may be a column
+    slice), ``up``: [C, R]."""
+    lp, ldl = _slice(low, "gla_decay low")
+    _want(up, "gla_decay up", ndim=2)
+    _want(out, "gla_decay out", torch.float32, 2)
+    T, R = low.shape
+    C = up.shape[0]
+    if up.shape[1] != R or out.shape != (T, C):
+        raise KernelError(f"gla_decay: low {tuple(low.shape)}, up {tuple(up.shape)}, out {tuple(out.shape)}")
+    if bias is not None:
+        _want(bias, "gla_decay bias", torch.float32, 1)
+        if bias.numel() != C:
+            raise KernelError(f"gla_decay: a bias of {bias.numel()} values for {C} channels")
+    lib = library("linear_attention")
+    _check(lib, lib.lp_gla_decay(lp, ldl, up.data_ptr(), _code(up, "gla_decay up"), _ptr(bias), out.data_ptr(), T, C, R,
+                                 float(tau), _stream()))
+    return out
+
+
+def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torch.Tensor, state: torch.Tensor,
+             slots: torch.Tensor, q_start: torch.Tensor, out: torch.Tensor, *, num_heads: int, key_dim: int,
+             value_dim: int, q_scale: float) -> torch.Tensor:
+    """The recurrence S <- diag(decay_t) S + k_t v_t^T, out_t = S^T (q_t * q_scale) over the step's tokens of every
+    sequence, from and into ``state`` float32 [slots, H, dk, dv] (row ``slots[b]`` for sequence b). ``proj``: float32
+    [T, F] with queries, keys and values at the given columns; ``decay``: float32 [T, H * dk]; ``out``: float32 [T, H * dv]."""
+    _want(proj, "gla_scan proj", torch.float32, 2)
+    _want(decay, "gla_scan decay", torch.float32, 2)
+    _want(state, "gla_scan state", torch.float32, 4)
+    _want(slots, "gla_scan slots", torch.int32, 1)
+    _want(q_start, "gla_scan q_start", torch.int32, 1)
+    _want(out, "gla_scan out", torch.float32, 2)
+    T = proj.shape[0]
+    H, dk, dv = num_heads, key_dim, value_dim
+    B = slots.numel()
+    if (decay.shape != (T, H * dk) or state.shape[1:] != (H, dk, dv) or out.shape != (T, H * dv)
+            or q_start.numel() != B + 1):
+        raise KernelError(f"gla_scan: proj {tuple(proj.shape)}, decay {tuple(decay.shape)}, state {tuple(state.shape)}, "
+                          f"out {tuple(out.shape)}, {B} sequences")
+    lib = library("linear_attention")
+    _check(lib, lib.lp_gla_scan(proj.data_ptr(), proj.shape[1], int(q_off), int(k_off), int(v_off), decay.data_ptr(),
+                                state.data_ptr(), slots.data_ptr(), q_start.data_ptr(), out.data_ptr(), B, H, dk, dv,
+                                float(q_scale), _stream()))
+    return out
+
+
+def gla_finish(o: torch.Tensor, gain: torch.Tensor, eps: float, gate: Optional[torch.Tensor], out: torch.Tensor, *,
+               num_heads: int, value_dim: int) -> torch.Tensor:
+    """out[t, h] = rmsnorm(o[t, h]) * gain * silu(gate[t, h]) per head of ``value_dim`` values; ``gate``: float32
+    [T, H * dv] (may be a column slice) or None."""
+    _want(o, "gla_finish o", torch.float32, 2)
+    _want(gain, "gla_finish gain", torch.float32, 1)
+    _want(out, "gla_finish out", ndim=2)
+    T = o.shape[0]
+    if o.shape != (T, num_heads * value_dim) or out.shape != o.shape or gain.numel() != value_dim:
+        raise KernelError(f"gla_finish: o {tuple(o.shape)}, out {tuple(out.shape)}, gain {tuple(gain.shape)}")
+    gp, ldg = (None, 0)
+    if gate is not None:
+        gp, ldg = _slice(gate, "gla_finish gate")
+        if gate.shape != o.shape:
+            raise KernelError(f"gla_finish: gate {tuple(gate.shape)} does not match o {tuple(o.shape)}")
+    lib = library("linear_attention")
+    _check(lib, lib.lp_gla_finish(o.data_ptr(), gain.data_ptr(), float(eps), gp, ldg, out.data_ptr(),
+                                  _code(out, "gla_finish out"), T, num_heads, value_dim, _stream()))
+    return out
 
 
 # --------------------------------------------------------------------------- sampling

@@ -1,18 +1,23 @@
 """One layer: the arrangement of its norms, its mixer and its feed-forward.
 
+``parallel``: x += gate * mixer(norm(x)) + gate * feed_forward(norm(x)) from one norm, optionally followed by a
+weighted sum over the results of all layers so far (:class:`ParallelBlock`).
+
 ``prenorm``: x += mixer(norm(x)); x += feed_forward(norm(x)), the residual stream
 x in float32 (inference/TransformerBlock.java:73-78, :109, :116-122, :149).
 """
 from __future__ import annotations
 
 import inspect
-from typing import Dict, Mapping
+from typing import Dict, Mapping, Optional
 
 import torch
 
 from ..kernels import ops
 from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, FollowingNorm, Part, PendingNorm, Runtime
-from .specs import BlockSpec, TensorSpec
+from ..errors import ConfigError
+from .linear import Linear
+from .specs import BIAS, MATRIX, BlockSpec, ParallelBlockSpec, TensorSpec
 
 
 class PreNormBlock(Part):
@@ -120,4 +125,120 @@ class PreNormBlock(Part):
                 norm.apply(residual, h)
 
 
+class ParallelBlock(Part):
+    """x <- x + gate_m * mixer(h) + gate_f * ffn(h) with h = norm(x): one norm, both sublayers read its output.
+    Each gate (optional) is sigmoid(W h + b) per feature. With a depth mix, the layer's result X is kept and the
+    stream that goes on is sum_j w[j] X_j over the embedding's output X_0 and every layer's result so far.
+
+    Everything that multiplies h (the mixer's input projections if it offers them, the gates, the feed-forward's
+    up projection) is stacked into one matrix, so a layer forms all of them in one product with float32 sums;
+    gates, residual sum and depth mix are one kernel at the end. A mixer or feed-forward without those hooks
+    is run through its ordinary ``forward`` into a zeroed buffer."""
+
+    def __init__(self, spec: ParallelBlockSpec):
+        self.spec = spec
+        self.norm = NORMS.build(spec.norm)
+        self.mixer = MIXERS.build(spec.mixer)
+        self.ffn = FEED_FORWARDS.build(spec.ffn) if spec.ffn is not None else None
+        if spec.ffn_gate is not None and spec.ffn is None:
+            raise ConfigError("a gate for a feed-forward that the layer does not have")
+        if spec.depth_mix is not None and not 2 <= spec.depth_mix.count <= spec.depth_mix.total:
+            raise ConfigError(f"a depth mix over {spec.depth_mix.count} of {spec.depth_mix.total} streams")
+        self.proj: Optional[Linear] = None
+
+    def children(self):
+        return tuple(p for p in (self.norm, self.mixer, self.ffn) if p is not None)
+
+    @property
+    def capture_safe(self) -> bool:
+        return all(bool(getattr(part, "capture_safe", False)) for part in self.children())
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        s = self.spec
+        d = s.norm.size
+        out: Dict[str, TensorSpec] = {}
+        out.update(self.norm.tensor_specs())
+        out.update(self.mixer.tensor_specs())
+        if self.ffn is not None:
+            out.update(self.ffn.tensor_specs())
+        for gate in (s.mixer_gate, s.ffn_gate):
+            if gate is not None:
+                out[gate.weight] = TensorSpec((d, d), MATRIX)
+                out[gate.bias] = TensorSpec((d,), BIAS)
+        if s.depth_mix is not None:
+            out[s.depth_mix.weights] = TensorSpec((s.depth_mix.count,), BIAS)
+        return out
+
+    def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
+        super().load(tensors, runtime)
+        s = self.spec
+        for part in self.children():
+            part.load(tensors, runtime)
+        stacked, at = [], 0
+        self._mixer_at = self._mixer_gate_at = self._ffn_gate_at = self._up_at = None
+        if hasattr(self.mixer, "input_projections"):
+            self._mixer_at = at
+            for m in self.mixer.input_projections():
+                stacked.append(m)
+                at += m.shape[0]
+        self.mixer_gate_bias = self.ffn_gate_bias = None
+        if s.mixer_gate is not None:
+            self._mixer_gate_at, at = at, at + tensors[s.mixer_gate.weight].shape[0]
+            stacked.append(tensors[s.mixer_gate.weight])
+            self.mixer_gate_bias = runtime.gain(tensors[s.mixer_gate.bias])
+        if s.ffn_gate is not None:
+            self._ffn_gate_at, at = at, at + tensors[s.ffn_gate.weight].shape[0]
+            stacked.append(tensors[s.ffn_gate.weight])
+            self.ffn_gate_bias = runtime.gain(tensors[s.ffn_gate.bias])
+        if self.ffn is not None and hasattr(self.ffn, "up_matrix"):
+            self._up_at, at = at, at + self.ffn.up_matrix().shape[0]
+            stacked.append(self.ffn.up_matrix())
+        self.proj = Linear(stacked, runtime) if stacked else None
+        self.depth_weights = runtime.gain(tensors[s.depth_mix.weights]) if s.depth_mix is not None else None
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
+    def forward(self, ctx, cache, residual: torch.Tensor) -> bool:
+        s, act = self.spec, self.runtime.act_dtype
+        T, d = residual.shape
+        h = ctx.buffer("normed", (T, d), act)
+        with ops.section("norm"):
+            self.norm.apply(residual, h)
+        proj = None
+        if self.proj is not None:
+            proj = ctx.buffer("layer_proj", (T, self.proj.out_features), torch.float32)
+            with ops.section("layer.proj"):
+                self.proj.store(h, proj, ctx)
+        m = ctx.buffer("mixer_out", (T, d), torch.float32)
+        if self._mixer_at is not None:
+            self.mixer.forward_projected(ctx, cache, proj, self._mixer_at, m)
+        else:
+            m.zero_()
+            self.mixer.forward(ctx, cache, h, m)
+        f = None
+        if self.ffn is not None:
+            f = ctx.buffer("ffn_out", (T, d), torch.float32)
+            if self._up_at is not None:
+                width = self.ffn.up_matrix().shape[0]
+                self.ffn.forward_from_up(ctx, proj[:, self._up_at:self._up_at + width], f)
+            else:
+                f.zero_()
+                self.ffn.forward(ctx, h, f)
+        m_gate = f_gate = None
+        if self._mixer_gate_at is not None:
+            m_gate = (proj[:, self._mixer_gate_at:self._mixer_gate_at + d], self.mixer_gate_bias)
+        if self._ffn_gate_at is not None:
+            f_gate = (proj[:, self._ffn_gate_at:self._ffn_gate_at + d], self.ffn_gate_bias)
+        with ops.section("layer.sum"):
+            if s.depth_mix is not None:
+                streams = ctx.buffer("depth_streams", (s.depth_mix.total, T, d), torch.float32)
+                ops.gated_sum(residual, m, m_gate, f, f_gate, streams=streams, mix=self.depth_weights,
+                              count=s.depth_mix.count, keep_input=s.depth_mix.count == 2)
+            else:
+                ops.gated_sum(residual, m, m_gate, f, f_gate)
+        return False
+
+
 BLOCKS.register("prenorm", PreNormBlock)
+BLOCKS.register("parallel", ParallelBlock)

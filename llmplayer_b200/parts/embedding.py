@@ -33,7 +33,7 @@ class Embedding(Part):
 
     def forward(self, tokens: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         with ops.section("embedding"):
-            return ops.embed(self.table, tokens, out)
+            return ops.embed(self.table, tokens, out, self.spec.scale)
 
 class LinearHead(Part):
     def __init__(self, spec: HeadSpec):

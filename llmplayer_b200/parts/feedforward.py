@@ -14,7 +14,7 @@ import torch
 
 from .base import FEED_FORWARDS, Part, PendingNorm, Runtime
 from .linear import Linear
-from .specs import MATRIX, SwiGLUSpec, TensorSpec
+from .specs import BIAS, MATRIX, SwiGLUSpec, TensorSpec, XIELUSpec
 
 
 class SwiGLU(Part):
@@ -63,3 +63,71 @@ class SwiGLU(Part):
 
 
 FEED_FORWARDS.register("swiglu", SwiGLU)
+
+
+class XIELUFeedForward(Part):
+    """down(act(up x)) with act(z) = softplus(p) z^2 + z / 2 for z > 0 and (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2
+    otherwise; p and q are the layer's tensor ``act``. The activation is evaluated in float32 on the float32
+    sums of the up projection.
+
+    A block that projects its normed input for several consumers at once may take this part's ``up`` matrix
+    into that product (:meth:`up_matrix`) and hand the sums to :meth:`forward_from_up`."""
+    capture_safe = True
+
+    def __init__(self, spec: XIELUSpec):
+        self.spec = spec
+        self.up: Optional[Linear] = None
+        self.down: Optional[Linear] = None
+        self.numbers: Optional[torch.Tensor] = None
+        self._up_host = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        s = self.spec
+        return {
+            s.up: TensorSpec((s.intermediate_size, s.hidden_size), MATRIX),
+            s.down: TensorSpec((s.hidden_size, s.intermediate_size), MATRIX),
+            s.act: TensorSpec((2,), BIAS),
+        }
+
+    def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
+        super().load(tensors, runtime)
+        s = self.spec
+        self._up_host = tensors[s.up]
+        self.down = Linear([tensors[s.down]], runtime)
+        self.numbers = runtime.gain(tensors[s.act])
+
+    def up_matrix(self):
+        """The host tensor of the up projection, for a block that stacks it into a wider product."""
+        return self._up_host
+
+    def _own_up(self) -> Linear:
+        if self.up is None:
+            self.up = Linear([self._up_host], self.runtime)
+        return self.up
+
+    def forward_from_up(self, ctx, z: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """``z``: the float32 sums up x [T, F] (may be a column slice); writes down(act(z)) to ``out`` float32 [T, d]."""
+        from ..kernels import ops
+        h = ctx.buffer("ffn_hidden", (z.shape[0], self.spec.intermediate_size), self.runtime.act_dtype)
+        with ops.section("ffn.act"):
+            ops.xielu(z, self.numbers, h)
+        with ops.section("ffn.down"):
+            self.down.store(h, out, ctx)
+        return out
+
+    def forward(self, ctx, x, residual: torch.Tensor) -> bool:
+        from ..kernels import ops
+        if isinstance(x, PendingNorm):
+            x = x.tensor()
+        T = x.shape[0]
+        z = ctx.buffer("ffn_up", (T, self.spec.intermediate_size), torch.float32)
+        with ops.section("ffn.up"):
+            self._own_up().store(x, z, ctx)
+        out = ctx.buffer("ffn_out", tuple(residual.shape), torch.float32)
+        self.forward_from_up(ctx, z, out)
+        with ops.section("ffn.add"):
+            ops.gated_sum(residual, out)
+        return False
+
+
+FEED_FORWARDS.register("xielu", XIELUFeedForward)

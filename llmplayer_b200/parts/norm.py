@@ -1,4 +1,5 @@
-"""RMS norm: out = x / sqrt(mean(x^2) + eps) * gain, in float32.
+"""Norms of the residual stream, in float32: RMS norm, out = x / sqrt(mean(x^2) + eps) * gain, and
+layer norm with a gain and no bias.
 
 Reference: inference/RMSNorm.java:17-35, tensor/ScalarOps.java:26-35,
 src/main/resources/kernels/cuda/rmsnorm.cu:6-46. The gain is used as stored.
@@ -9,6 +10,7 @@ from typing import Dict, Mapping, Optional
 
 import torch
 
+from ..errors import ConfigError
 from ..kernels import ops
 from .base import NORMS, Part, Runtime
 from .specs import GAIN, NormSpec, TensorSpec
@@ -36,4 +38,27 @@ class RMSNorm(Part):
         return ops.rmsnorm(x, self.weight, self.spec.eps, out, rows=rows, add=add, clear=clear)
 
 
+class LayerNorm(Part):
+    """out = (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * gain, in float32; no bias."""
+    capture_safe = True
+
+    def __init__(self, spec: NormSpec):
+        self.spec = spec
+        self.weight: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {self.spec.weight: TensorSpec((self.spec.size,), GAIN)}
+
+    def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
+        super().load(tensors, runtime)
+        self.weight = runtime.gain(tensors[self.spec.weight])
+
+    def apply(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None,
+              add: Optional[torch.Tensor] = None, clear: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if add is not None or clear is not None:
+            raise ConfigError("the layer norm kernel neither adds a residual nor clears a buffer on the side")
+        return ops.layernorm(x, self.weight, self.spec.eps, out, rows=rows)
+
+
 NORMS.register("rmsnorm", RMSNorm)
+NORMS.register("layernorm", LayerNorm)

@@ -19,17 +19,32 @@ from typing import Optional, Tuple
 MATRIX = "matrix"   # [out, in] weight of a linear map, or an embedding table
 GAIN = "gain"       # per-feature multiplier of a norm, drawn around one
 INTEGER = "integer"  # integer table, held as int32
+BIAS = "bias"       # additive vector or a handful of learned numbers, drawn around zero, used in float32
+
+
+ANY = -1            # a size that the model file decides: the loader accepts whatever it finds there
 
 
 @dataclass(frozen=True)
 class TensorSpec:
-    """Shape and kind of one named tensor of a model folder."""
+    """Shape and kind of one named tensor of a model folder. A size of ``ANY`` is read off the file
+    (``fill`` is what a writer of random weights puts there)."""
     shape: Tuple[int, ...]
     kind: str = MATRIX
+    fill: int = 16
+
+    def fits(self, shape) -> bool:
+        shape = tuple(shape)
+        return len(shape) == len(self.shape) and all(w == ANY or w == g for w, g in zip(self.shape, shape))
+
+    def concrete(self) -> Tuple[int, ...]:
+        return tuple(self.fill if w == ANY else w for w in self.shape)
 
 
 @dataclass(frozen=True)
 class NormSpec:
+    """``kind="rmsnorm"``: x / sqrt(mean(x^2) + eps) * weight. ``kind="layernorm"``: (x - mean) /
+    sqrt(variance + eps) * weight, the variance being the mean squared deviation; no bias."""
     size: int
     eps: float
     weight: str
@@ -96,6 +111,107 @@ class SwiGLUSpec:
 
 
 @dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Softmax attention whose keys and values are linear maps of one cached low-rank latent per position.
+
+    The down projection ``kv_down`` yields ``kv_rank + rope_dim`` values: the first ``kv_rank``, RMS-normed
+    with ``latent_norm``, are the latent; the rest are one rotated key part shared by all heads. Head h's
+    unrotated key is ``k_up`` [h] times the latent, its value ``v_up`` [h] times the latent; a query head is
+    laid out [``nope_dim`` unrotated | ``rope_dim`` rotated]. ``position`` rotates the ``rope_dim`` part.
+    ``out_gate`` (optional): a matrix [heads, hidden] whose sigmoid scales each head's output.
+    """
+    hidden_size: int
+    num_heads: int
+    nope_dim: int
+    rope_dim: int
+    value_dim: int
+    kv_rank: int
+    scale: float
+    norm_eps: float
+    position: PositionSpec
+    q: str
+    kv_down: str
+    latent_norm: str
+    k_up: str
+    v_up: str
+    o: str
+    out_gate: Optional[str] = None
+    kind: str = "latent_attention"
+
+
+@dataclass(frozen=True)
+class LowRankDecaySpec:
+    """A decay per key channel from the layer's input: sigmoid(up(down(x)) + bias)^(1 / temperature).
+    The width of the factor is read off ``down``'s shape."""
+    temperature: float
+    down: str
+    up: str
+    bias: str
+
+
+@dataclass(frozen=True)
+class GatedLinearAttentionSpec:
+    """Linear attention with a matrix state per head, S <- diag(decay) S + k v^T, o = S^T q, queries
+    scaled by ``key_dim`` ** -0.5; each head's output is RMS-normed over ``value_dim`` with the shared gain
+    ``out_norm``, multiplied by silu(``gate`` x) and projected by ``o``."""
+    hidden_size: int
+    num_heads: int
+    key_dim: int
+    value_dim: int
+    norm_eps: float
+    decay: LowRankDecaySpec
+    q: str
+    k: str
+    v: str
+    gate: str
+    out_norm: str
+    o: str
+    kind: str = "gated_linear_attention"
+
+
+@dataclass(frozen=True)
+class XIELUSpec:
+    """Dense feed-forward down(act(up x)) with the xIELU activation, whose two learned numbers are the
+    tensor ``act`` [2]."""
+    hidden_size: int
+    intermediate_size: int
+    up: str
+    down: str
+    act: str
+    kind: str = "xielu"
+
+
+@dataclass(frozen=True)
+class ResidualGateSpec:
+    """sigmoid(weight x + bias), one value per feature, multiplying a sublayer's result."""
+    weight: str
+    bias: str
+
+
+@dataclass(frozen=True)
+class DepthMixSpec:
+    """After a layer, the stream becomes a weighted sum of the embedding's output and of every layer's result
+    so far: ``weights`` [count] with count = 2 + the number of layers before this one."""
+    weights: str
+    count: int
+    total: int          # streams of the whole model (layers + 1): the size of the buffer all layers share
+
+
+@dataclass(frozen=True)
+class ParallelBlockSpec:
+    """One layer with one norm whose output both sublayers read: x + mixer(norm(x)) + ffn(norm(x)).
+    ``ffn`` may be None. Each sublayer's result may be gated (:class:`ResidualGateSpec`, from the same
+    normed input); ``depth_mix`` replaces the result by a weighted sum over depth."""
+    norm: NormSpec
+    mixer: object
+    ffn: Optional[object] = None
+    mixer_gate: Optional[ResidualGateSpec] = None
+    ffn_gate: Optional[ResidualGateSpec] = None
+    depth_mix: Optional[DepthMixSpec] = None
+    kind: str = "parallel"
+
+
+@dataclass(frozen=True)
 class BlockSpec:
     """One layer: how its norms, mixer and feed-forward are arranged.
 
@@ -110,10 +226,12 @@ class BlockSpec:
 
 @dataclass(frozen=True)
 class EmbeddingSpec:
+    """The token's row of the table, times ``scale``."""
     vocab_size: int
     hidden_size: int
     weight: str
     kind: str = "embedding"
+    scale: float = 1.0
 
 
 @dataclass(frozen=True)

@@ -12,7 +12,7 @@ from typing import Dict, Mapping
 import torch
 
 from ..errors import WeightError
-from ..parts.specs import GAIN, INTEGER, MATRIX, TensorSpec
+from ..parts.specs import BIAS, GAIN, INTEGER, MATRIX, TensorSpec
 from .safetensors_io import open_model_files
 
 _FLOATS = ("F32", "BF16", "F16", "F64")
@@ -37,11 +37,12 @@ def load_tensors(model_dir: str, expected: Mapping[str, TensorSpec]) -> Dict[str
                 missing.append(name)
                 continue
             dtype, shape = owners[name].info(name)
-            if tuple(shape) != tuple(spec.shape):
-                wrong.append(f"{name}: expected shape {list(spec.shape)}, file has {list(shape)}")
+            if not spec.fits(shape):
+                wanted = ["any" if w < 0 else w for w in spec.shape]
+                wrong.append(f"{name}: expected shape {wanted}, file has {list(shape)}")
             elif spec.kind == INTEGER and dtype not in _INTS:
                 wrong.append(f"{name}: expected an integer table, file has dtype {dtype}")
-            elif spec.kind in (MATRIX, GAIN) and dtype not in _FLOATS:
+            elif spec.kind in (MATRIX, GAIN, BIAS) and dtype not in _FLOATS:
                 wrong.append(f"{name}: expected floating-point values, file has dtype {dtype}")
         unexpected = sorted(n for n in owners if n not in expected)
         if missing or wrong or unexpected:

@@ -16,7 +16,7 @@ import torch
 
 from ..config.registry import ArchitectureConfig
 from ..errors import WeightError
-from ..parts.specs import GAIN, INTEGER, MATRIX, TensorSpec
+from ..parts.specs import BIAS, GAIN, INTEGER, MATRIX, TensorSpec
 from .safetensors_io import write_safetensors
 
 _STORE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
@@ -30,13 +30,14 @@ def random_tensors(expected: Mapping[str, TensorSpec], seed: int, std: float = 0
     gen.manual_seed(int(seed))
     out: Dict[str, torch.Tensor] = {}
     for name, spec in expected.items():
+        shape = spec.concrete()
         if spec.kind == INTEGER:
-            out[name] = torch.zeros(spec.shape, dtype=torch.int32)
+            out[name] = torch.zeros(shape, dtype=torch.int32)
             continue
-        draw = torch.randn(spec.shape, generator=gen, dtype=torch.float32) * std
+        draw = torch.randn(shape, generator=gen, dtype=torch.float32) * std
         if spec.kind == GAIN:
             draw += 1.0
-        elif spec.kind != MATRIX:
+        elif spec.kind not in (MATRIX, BIAS):
             raise WeightError(f"tensor {name!r}: unknown kind {spec.kind!r}")
         out[name] = draw.to(_STORE[dtype])
     return out
