@@ -2,6 +2,7 @@
 """Benchmark: decode tokens per second of a Llama shape with random bf16 weights, through ``Engine.generate``.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--shape 1b|3b|8b]
+    python bench.py --design ramupel [--size s|m|l] [--layers N]      (the hybrid design beside Llama at equal size)
 
 One "step" is one decode step of the whole batch. The default run has the Llama-3.2-1B shape, a batch of 8
 sequences with 512-token prompts in a cache sized for a context of 4096. Every figure comes from the library's
@@ -18,6 +19,11 @@ the laps is reported. It prints ONE JSON line:
 ``--shape 3b`` / ``8b`` run the other two shapes the baseline names (batch 16 with prompts of 64 to 1,024 tokens
 and 256 steps; batch 32 with 2,048-token prompts and 512 steps) unless ``--steps`` says otherwise.
 ``--profile`` adds the device time per section of the model walk (a separate, short run in profile mode).
+
+``--design ramupel`` measures something else and leaves the default workload alone: prefill (one 2,048-token prompt)
+and decode (batch 8 from 512-token prompts) throughput of the Ramupel design at a few layer sizes, beside a Llama of
+the same width, depth, head count and feed-forward parameters, both with random weights, plus the device time per
+section of the model walk of each and what the mixers' core kernels reach of their rooflines.
 """
 from __future__ import annotations
 
@@ -140,6 +146,147 @@ def prefill_flops(cfg, layers, lengths):
     return 2.0 * layers * layer_weights(cfg) * tokens + attention + 2.0 * cfg["vocab_size"] * cfg["hidden_size"] * len(lengths)
 
 
+# ------------------------------------------------------------------ the hybrid design beside Llama
+# name -> (width, heads, latent (dim, rot_dim, vdim, kv_rank), gla (heads, dim, vdim), feed-forward width)
+HYBRID_SIZES = {
+    "s": (1024, 8, (64, 32, 64, 256), (4, 64, 256), 4096),
+    "m": (2048, 16, (128, 64, 128, 512), (8, 128, 256), 8192),
+    "l": (4096, 32, (128, 64, 128, 512), (16, 128, 256), 14336),
+}
+
+
+def hybrid_configs(size, layers):
+    width, heads, (dn, dr, dv, rank), (gh, gk, gv), ff = HYBRID_SIZES[size]
+    latent = {"type": "latent_attention", "mlp": {"kind": "dense", "ff": ff},
+              "mixer": {"heads": heads, "dim": dn, "rot_dim": dr, "vdim": dv, "kv_rank": rank, "scale": (dn + dr) ** -0.5,
+                        "rot": {"base": 10000.0, "dims": dr}}}
+    gla = {"type": "gla", "mlp": {"kind": "dense", "ff": ff}, "mixer": {"heads": gh, "dim": gk, "vdim": gv, "tau": 16.0}}
+    ramupel = {"architecture": "Ramupel", "vocab": 32000, "width": width, "embedding": {"scale": float(width) ** 0.5},
+               "norm": {"eps": 1e-5}, "layers": [gla if i % 4 == 0 else latent for i in range(layers)]}
+    # the same feed-forward parameters in three matrices instead of two
+    llama = llama_shape(layers, width, heads, max(1, heads // 4), width // heads, (2 * ff // 3 + 127) // 128 * 128, 8.0, True)
+    llama["vocab_size"] = 32000
+    return ramupel, llama
+
+
+def compare_designs(args, peaks) -> int:
+    import torch
+    from llmplayer_b200 import Engine
+    from llmplayer_b200.config import config_from_dict
+    from llmplayer_b200.sampling import SamplerConfig
+    from llmplayer_b200.weights import write_random_model
+    layers = args.layers or 4
+    repeats = max(1, args.repeats)
+    steps = args.steps or 64
+    warmup = max(3, args.warmup)
+    prompt, batch, prefill_len = args.prompt_len or 512, args.batch or 8, 2048
+    context = max(prefill_len, prompt + warmup + repeats * steps + 2)
+    gen = torch.Generator().manual_seed(5)
+    clocks = ClockSampler()
+    clocks.start()
+    out = {"metric": "prefill and decode tok/s of the Ramupel design beside Llama at equal size (bf16)", "impl": "ours",
+           "layers": layers, "batch": batch, "prompt_len": prompt, "prefill_len": prefill_len, "peaks": peaks, "sizes": {}}
+    try:
+        for size in ([args.size] if args.size else sorted(HYBRID_SIZES, key="sml".index)):
+            row = {}
+            for name, raw in zip(("ramupel", "llama"), hybrid_configs(size, layers)):
+                vocab = raw.get("vocab", raw.get("vocab_size"))
+                tmp = tempfile.mkdtemp(prefix="llmplayer_b200_bench_")
+                try:
+                    write_random_model(config_from_dict(raw), 7, tmp, dtype="bfloat16")
+                    engine = Engine.load(tmp, dtype="bfloat16", context_length=context, max_batch=batch)
+                    profiled = Engine.load(tmp, dtype="bfloat16", context_length=context, max_batch=batch, profile=True)
+                finally:
+                    shutil.rmtree(tmp, ignore_errors=True)
+
+                def tokens(n):
+                    return torch.randint(0, vocab, (n,), generator=gen).tolist()
+                begin = time.time()
+                times = []
+                long_prompt = tokens(prefill_len)
+                for i in range(2 + repeats):
+                    slot = engine.acquire()
+                    torch.cuda.synchronize()
+                    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    start.record()
+                    engine.step([(slot, long_prompt)], [[prefill_len - 1]])
+                    stop.record()
+                    torch.cuda.synchronize()
+                    engine.release(slot)
+                    if i >= 2:
+                        times.append(start.elapsed_time(stop))
+                prefill_ms = statistics.median(times)
+                ps = [tokens(prompt) for _ in range(batch)]
+                engine.generate(ps, SamplerConfig.greedy(), max_tokens=warmup + repeats * steps + 1, stop_token_ids=(),
+                                laps=(warmup, steps))
+                laps = engine.last_generation_stats.laps
+                decode_ms = statistics.median(lap["device_ms"] / lap["steps"] for lap in laps)
+                engine.check()
+                end = time.time()
+                # sections: one prompt alone, then decode steps alone (profile mode: no graphs, no overlap)
+                slot = profiled.acquire()
+                profiled.step([(slot, long_prompt)], [[prefill_len - 1]])
+                profiled.release(slot)
+                profiled.profile_report(reset=True)
+                slot = profiled.acquire()
+                profiled.step([(slot, long_prompt)], [[prefill_len - 1]])
+                profiled.release(slot)
+                pre = profiled.profile_report(reset=True)
+                slots = [profiled.acquire() for _ in ps]
+                profiled.step(list(zip(slots, ps)), [[prompt - 1]] * batch)
+                for _ in range(4):
+                    profiled.step([(s, [1]) for s in slots], [[0]] * batch)
+                profiled.profile_report(reset=True)
+                for _ in range(16):
+                    profiled.step([(s, [1]) for s in slots], [[0]] * batch)
+                dec = profiled.profile_report(reset=True)
+                row[name] = {
+                    "prefill_tok_s": prefill_len / (prefill_ms / 1e3), "prefill_ms": prefill_ms,
+                    "decode_tok_s": batch / (decode_ms / 1e3), "decode_ms_per_step": decode_ms,
+                    "clocks": clocks.window(begin, end),
+                    "prefill_sections_ms": {k: round(v["ms_per_step"], 4) for k, v in pre["sections"].items()},
+                    "decode_sections_ms": {k: round(v["ms_per_step"], 4) for k, v in dec["sections"].items()},
+                }
+                del engine, profiled
+                torch.cuda.empty_cache()
+            row["rooflines"] = hybrid_rooflines(size, layers, row, peaks, batch, prompt + 10, prefill_len)
+            out["sizes"][size] = row
+        print(json.dumps(out))
+        return 0
+    finally:
+        clocks.stop()
+
+
+def hybrid_rooflines(size, layers, row, peaks, batch, context, n):
+    """What the mixers' core kernels reach of their rooflines, per layer that has them: prompt kernels against the
+    bf16 tensor peak (algorithmic FLOPs / time), decode kernels against the copy bandwidth (bytes they must read)."""
+    width, heads, (dn, dr, dv, rank), (gh, gk, gv), ff = HYBRID_SIZES[size]
+    n_gla = sum(1 for i in range(layers) if i % 4 == 0)
+    n_lat = layers - n_gla
+    flops, gbs = peaks["bf16_tflops"] * 1e12, peaks["hbm_gbs"] * 1e9
+    r, l = row["ramupel"], row["llama"]
+    hd, G = width // heads, max(1, heads // 4)
+    out = {}
+
+    def frac(work, ms, count, peak):
+        return None if not ms or not count else work / (ms / count / 1e3) / peak
+    # prompt attention: causal scores and weighted sums
+    out["prefill latent attention (of tensor peak)"] = frac(
+        heads * n * (n + 1) * ((rank + dr) + rank), r["prefill_sections_ms"].get("attention.scores"), n_lat, flops)
+    out["prefill llama attention (of tensor peak)"] = frac(
+        heads * n * (n + 1) * 2 * hd, l["prefill_sections_ms"].get("attention.scores"), layers, flops)
+    out["prefill gla recurrence (of tensor peak)"] = frac(
+        6.0 * gh * gk * gv * n, r["prefill_sections_ms"].get("recurrence.scan"), n_gla, flops)
+    # decode: the cached rows / keys and values / states that must be read (and states written)
+    out["decode latent attention (of copy bandwidth)"] = frac(
+        batch * context * (rank + dr) * 2, r["decode_sections_ms"].get("attention.scores"), n_lat, gbs)
+    out["decode llama attention (of copy bandwidth)"] = frac(
+        batch * context * 2 * G * hd * 2, l["decode_sections_ms"].get("attention.scores"), layers, gbs)
+    out["decode gla recurrence (of copy bandwidth)"] = frac(
+        batch * gh * gk * gv * 4 * 2, r["decode_sections_ms"].get("recurrence.scan"), n_gla, gbs)
+    return out
+
+
 def spread(values):
     return {"median": statistics.median(values), "min": min(values), "max": max(values), "repeats": len(values)}
 
@@ -160,6 +307,9 @@ def main() -> int:
     ap.add_argument("--prefill-only", action="store_true",
                     help="measure only the 2,048-token prefill (small runs for profiling)")
     ap.add_argument("--profile", action="store_true", help="add the device time per section of the model walk")
+    ap.add_argument("--design", default="llama", choices=("llama", "ramupel"),
+                    help="ramupel: the hybrid design beside Llama at equal size (another workload; see the module text)")
+    ap.add_argument("--size", default=None, choices=sorted(HYBRID_SIZES), help="with --design ramupel: one size only")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -170,6 +320,8 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported by this single-GPU library")
         return 2
+    if args.design == "ramupel":
+        return compare_designs(args, load_peaks())
     args.warmup = max(3, args.warmup)
     repeats = max(1, args.repeats)
 

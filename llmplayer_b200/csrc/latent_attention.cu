@@ -31,7 +31,8 @@ latent_prepare_kernel(const float* __restrict__ proj, int ld, int q_off, int kv_
                       float eps, const float* __restrict__ inv_freq, int rot, const int* __restrict__ positions,
                       const int* __restrict__ seq_ids, const int* __restrict__ page_table, int pt_stride,
                       float* __restrict__ q_out, TKV* __restrict__ pages, int H, int dn, int dr, int rank,
-                      int page_size) {
+                      int page_size, __nv_bfloat16* __restrict__ latent_out, __nv_bfloat16* __restrict__ shared_out,
+                      __nv_bfloat16* __restrict__ q_half) {
     __shared__ float cs[128], sn[128];
     __shared__ float scratch[32];
     lp_grid_release();
@@ -49,7 +50,11 @@ latent_prepare_kernel(const float* __restrict__ proj, int ld, int q_off, int kv_
     const int page = page_table[(long long)seq_ids[t] * pt_stride + pos / page_size];
     const int Dk = rank + dr;
     TKV* dst = pages + ((long long)page * page_size + pos % page_size) * Dk;
-    for (int i = tid; i < rank; i += blockDim.x) dst[i] = lp_from_float<TKV>(kv[i] * factor * gain[i]);
+    for (int i = tid; i < rank; i += blockDim.x) {
+        const float c = kv[i] * factor * gain[i];
+        dst[i] = lp_from_float<TKV>(c);
+        if (latent_out) latent_out[(long long)t * rank + i] = __float2bfloat16_rn(c);
+    }
     // the shared key part: pairs (i, i + half) of its first `rot` values turn, the rest pass
     const float* kr = kv + rank;
     for (int i = tid; i < dr; i += blockDim.x) {
@@ -57,6 +62,7 @@ latent_prepare_kernel(const float* __restrict__ proj, int ld, int q_off, int kv_
         if (i < half) v = __fsub_rn(__fmul_rn(kr[i], cs[i]), __fmul_rn(kr[i + half], sn[i]));
         else if (i < rot) v = __fadd_rn(__fmul_rn(kr[i], cs[i - half]), __fmul_rn(kr[i - half], sn[i - half]));
         dst[rank + i] = lp_from_float<TKV>(v);
+        if (shared_out) shared_out[(long long)t * dr + i] = __float2bfloat16_rn(v);
     }
     // queries: head by head [dn as projected | dr with the same rotation]
     const int hd = dn + dr;
@@ -70,6 +76,65 @@ latent_prepare_kernel(const float* __restrict__ proj, int ld, int q_off, int kv_
             else if (i < rot) v = __fadd_rn(__fmul_rn(q[e], cs[i - half]), __fmul_rn(q[e - half], sn[i - half]));
         }
         qo[e] = v;
+        if (q_half) q_half[(long long)t * H * hd + e] = __float2bfloat16_rn(v);
+    }
+}
+
+// ---------------------------------------------------------------- per-head keys and values of a prompt
+// For steps whose sequences all start at their first token, the heads' keys and values are formed outright
+// (one product with the stacked key and value maps) and laid out as pages of keys and values, so that the
+// tensor-core attention of ordinary heads serves: key of head h = [its unrotated part | the shared rotated
+// part], value of head h padded with zeros to the key's size. kv: bfloat16 [T, H * dn + H * dv].
+__global__ void __launch_bounds__(256)
+latent_heads_to_pages_kernel(const __nv_bfloat16* __restrict__ kv, const __nv_bfloat16* __restrict__ shared_part,
+                             const int* __restrict__ positions, const int* __restrict__ seq_ids,
+                             const int* __restrict__ table, int pt_stride, const int* __restrict__ kv_len,
+                             __nv_bfloat16* __restrict__ pages, int H, int dn, int dr, int dv, int page_size) {
+    lp_grid_release();
+    lp_grid_wait();
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const int hd = dn + dr;
+    const int seq = seq_ids[t];
+    const long long page = table[(long long)seq * pt_stride + pos / page_size];
+    __nv_bfloat16* kdst = pages + page * 2 * H * page_size * hd + (long long)(pos % page_size) * hd;
+    __nv_bfloat16* vdst = kdst + (long long)H * page_size * hd;
+    const __nv_bfloat16* row = kv + (long long)t * H * (dn + dv);
+    const __nv_bfloat16 zero = __float2bfloat16_rn(0.f);
+    for (int e = threadIdx.x; e < H * hd; e += blockDim.x) {
+        const int h = e / hd, i = e - h * hd;
+        const long long at = (long long)h * page_size * hd + i;
+        kdst[at] = i < dn ? row[h * dn + i] : shared_part[(long long)t * dr + i - dn];
+        vdst[at] = i < dv ? row[H * dn + h * dv + i] : zero;
+    }
+    // the sequence's last token also clears the rest of its last page: the attention kernel multiplies those rows
+    // by weights of zero, which only gives zero if the rows are finite
+    if (pos == kv_len[seq] - 1) {
+        const int rest = page_size - 1 - pos % page_size;
+        for (long long e = threadIdx.x; e < (long long)H * rest * hd; e += blockDim.x) {
+            const int h = (int)(e / ((long long)rest * hd));
+            const long long at = (long long)h * page_size * hd + hd + (e - (long long)h * rest * hd);
+            kdst[at] = zero;
+            vdst[at] = zero;
+        }
+    }
+}
+
+// out[t, h * dv + v] = heads[t, h * hd + v] * sigmoid(gate[t, h]): the first dv features of each head, gated.
+__global__ void __launch_bounds__(256)
+latent_gate_heads_kernel(const __nv_bfloat16* __restrict__ heads, const float* __restrict__ gate, int ldg,
+                         __nv_bfloat16* __restrict__ out, int T, int H, int hd, int dv) {
+    lp_grid_release();
+    lp_grid_wait();
+    const long long n = (long long)T * H * dv;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long th = i / dv;
+        const int v = (int)(i - th * dv);
+        const long long t = th / H;
+        const int h = (int)(th - t * H);
+        float x = __bfloat162float(heads[th * hd + v]);
+        if (gate) x *= 1.0f / (1.0f + expf(-gate[t * ldg + h]));
+        out[i] = __float2bfloat16_rn(x);
     }
 }
 
@@ -92,7 +157,7 @@ latent_absorb_kernel(const float* __restrict__ q, const TW* __restrict__ uk, flo
     }
     __syncthreads();
     const TW* u = uk + (long long)h * dn * rank;
-    for (int r = tid; r < rank; r += blockDim.x) {
+    for (int r = blockIdx.z * blockDim.x + tid; r < rank; r += gridDim.z * blockDim.x) {
         float acc[TOK_TILE];
 #pragma unroll
         for (int i = 0; i < TOK_TILE; ++i) acc[i] = 0.f;
@@ -105,7 +170,7 @@ latent_absorb_kernel(const float* __restrict__ q, const TW* __restrict__ uk, flo
         for (int i = 0; i < TOK_TILE; ++i)
             if (i < nt) qa[((long long)(t0 + i) * H + h) * Dk + r] = acc[i];
     }
-    for (int e = tid; e < nt * dr; e += blockDim.x) {
+    for (int e = blockIdx.z * blockDim.x + tid; e < nt * dr; e += gridDim.z * blockDim.x) {
         const int i = e / dr, d = e - i * dr;
         qa[((long long)(t0 + i) * H + h) * Dk + rank + d] = q[((long long)(t0 + i) * H + h) * hd + dn + d];
     }
@@ -245,38 +310,46 @@ template <typename TW, typename TOut>
 __global__ void __launch_bounds__(128)
 latent_expand_kernel(const float* __restrict__ part, int shares, const TW* __restrict__ uv,
                      const float* __restrict__ gate, int ldg, TOut* __restrict__ out, int T, int H, int rank, int dv) {
-    extern __shared__ float ls[];                         // [TOK_TILE][rank]
+    extern __shared__ float ls[];                         // [TOK_TILE][rank], then [TOK_TILE][shares] weights
     __shared__ float gs[TOK_TILE];
+    float* ws = ls + TOK_TILE * rank;
     lp_grid_release();
     lp_grid_wait();
     const int t0 = blockIdx.x * TOK_TILE, h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nt = min(TOK_TILE, T - t0);
-    for (int i = 0; i < TOK_TILE; ++i) {
-        if (i >= nt) {
-            for (int r = tid; r < rank; r += blockDim.x) ls[i * rank + r] = 0.f;
-            continue;
-        }
-        const float* p = part + ((long long)(t0 + i) * H + h) * shares * (rank + 2);
+    const int width = rank + 2;
+    // each share's weight e^(m_s - M) / sum_s l_s e^(m_s - M): a warp per token, lanes over shares
+    for (int i = warp; i < nt; i += 4) {
+        const float* p = part + ((long long)(t0 + i) * H + h) * shares * width;
         float M = -INFINITY;
-        for (int s = 0; s < shares; ++s) M = fmaxf(M, p[s * (rank + 2) + rank]);
+        for (int s = lane; s < shares; s += 32) M = fmaxf(M, p[s * width + rank]);
+        M = lp_warp_max(M);
         float L = 0.f;
-        for (int s = 0; s < shares; ++s) {
-            const float ms = p[s * (rank + 2) + rank];
-            if (ms != -INFINITY) L += p[s * (rank + 2) + rank + 1] * expf(ms - M);
+        for (int s = lane; s < shares; s += 32) {
+            const float ms = p[s * width + rank];
+            const float e = ms == -INFINITY ? 0.f : expf(ms - M);
+            ws[i * shares + s] = e;
+            L += p[s * width + rank + 1] * e;
         }
+        L = lp_warp_sum(L);
         const float inv = 1.0f / L;
-        for (int r = tid; r < rank; r += blockDim.x) {
-            float acc = 0.f;
-            for (int s = 0; s < shares; ++s) {
-                const float ms = p[s * (rank + 2) + rank];
-                if (ms != -INFINITY) acc = fmaf(p[s * (rank + 2) + r], expf(ms - M), acc);
-            }
-            ls[i * rank + r] = acc * inv;
-        }
-        if (tid == 0) gs[i] = gate ? 1.0f / (1.0f + expf(-gate[(long long)(t0 + i) * ldg + h])) : 1.0f;
+        for (int s = lane; s < shares; s += 32) ws[i * shares + s] *= inv;
+        if (lane == 0) gs[i] = gate ? 1.0f / (1.0f + expf(-gate[(long long)(t0 + i) * ldg + h])) : 1.0f;
     }
     __syncthreads();
-    for (int v = warp; v < dv; v += 4) {
+    for (int e = tid; e < TOK_TILE * rank; e += blockDim.x) {
+        const int i = e / rank, r = e - i * rank;
+        float acc = 0.f;
+        if (i < nt) {
+            const float* p = part + ((long long)(t0 + i) * H + h) * shares * width + r;
+            const float* wi = ws + i * shares;
+#pragma unroll 4
+            for (int s = 0; s < shares; ++s) acc = fmaf(p[(long long)s * width], wi[s], acc);
+        }
+        ls[e] = acc;
+    }
+    __syncthreads();
+    for (int v = blockIdx.z * 4 + warp; v < dv; v += gridDim.z * 4) {
         const TW* w = uv + ((long long)h * dv + v) * rank;
         float acc[TOK_TILE];
 #pragma unroll
@@ -310,11 +383,13 @@ int grant_shared(K kernel, size_t bytes, const char* what) {
 }  // namespace
 
 // proj: float32 [T, ld] with the queries at q_off ([H, dn + dr]) and the latent and shared key part at kv_off
-// ([rank + dr]); pages: [num_pages, page_size, rank + dr]; q_out: float32 [T, H, dn + dr].
+// ([rank + dr]); pages: [num_pages, page_size, rank + dr]; q_out: float32 [T, H, dn + dr]. Optional bfloat16
+// copies that lie together: latent_out [T, rank], shared_out [T, dr], q_half [T, H, dn + dr].
 extern "C" int lp_latent_prepare(const float* proj, int ld, int q_off, int kv_off, const float* gain, float eps,
                                  const float* inv_freq, int rot, const int* positions, const int* seq_ids,
                                  const int* page_table, int pt_stride, float* q_out, void* pages, int kv_dtype, int T,
-                                 int H, int dn, int dr, int rank, int page_size, cudaStream_t stream) {
+                                 int H, int dn, int dr, int rank, int page_size, void* latent_out, void* shared_out,
+                                 void* q_half, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || dn < 0 || dr < 0 || rank <= 0 || dn + dr <= 0) LP_REFUSE("latent_prepare: %d heads of %d + %d over rank %d", H, dn, dr, rank);
     if (rot < 0 || (rot & 1) || rot > dr || rot > 256) LP_REFUSE("latent_prepare: rotary width %d of %d (even, at most 256)", rot, dr);
@@ -324,7 +399,8 @@ extern "C" int lp_latent_prepare(const float* proj, int ld, int q_off, int kv_of
         LP_REFUSE("latent_prepare: slices at %d and %d do not fit rows of %d", q_off, kv_off, ld);
 #define LP_LAUNCH_PREP(TKV)                                                                                       \
     lp_launch(latent_prepare_kernel<TKV>, T, 256, 0, stream, proj, ld, q_off, kv_off, gain, eps, inv_freq, rot,    \
-              positions, seq_ids, page_table, pt_stride, q_out, (TKV*)pages, H, dn, dr, rank, page_size)
+              positions, seq_ids, page_table, pt_stride, q_out, (TKV*)pages, H, dn, dr, rank, page_size,                   \
+              (__nv_bfloat16*)latent_out, (__nv_bfloat16*)shared_out, (__nv_bfloat16*)q_half)
     if (kv_dtype == LP_F32) LP_LAUNCH_PREP(float);
     else if (kv_dtype == LP_BF16) LP_LAUNCH_PREP(__nv_bfloat16);
     else LP_REFUSE("latent_prepare: cache dtype code %d", kv_dtype);
@@ -337,7 +413,7 @@ extern "C" int lp_latent_absorb(const float* q, const void* uk, int w_dtype, flo
                                 int rank, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || H > 65535 || dn < 0 || dr < 0 || rank <= 0) LP_REFUSE("latent_absorb: %d heads of %d + %d over rank %d", H, dn, dr, rank);
-    dim3 grid((T + TOK_TILE - 1) / TOK_TILE, H);
+    dim3 grid((T + TOK_TILE - 1) / TOK_TILE, H, (rank + 127) / 128);
     const size_t smem = (size_t)TOK_TILE * (dn > 0 ? dn : 1) * sizeof(float);
     if (w_dtype == LP_F32) {
         if (grant_shared(latent_absorb_kernel<float>, smem, "latent_absorb")) return -1;
@@ -397,8 +473,12 @@ extern "C" int lp_latent_expand(const float* part, int shares, const void* uv, i
                                 void* out, int out_dtype, int T, int H, int rank, int dv, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || H > 65535 || rank <= 0 || dv <= 0 || shares <= 0) LP_REFUSE("latent_expand: %d heads, rank %d, values of %d, %d shares", H, rank, dv, shares);
-    dim3 grid((T + TOK_TILE - 1) / TOK_TILE, H);
-    const size_t smem = (size_t)TOK_TILE * rank * sizeof(float);
+    // few tokens: the value columns of a head are shared out over CTAs as well (each merges the shares itself)
+    const int tiles = (T + TOK_TILE - 1) / TOK_TILE;
+    int vparts = 1;
+    if (tiles * H < 2 * lp_sm_count()) vparts = min((dv + 15) / 16, max(1, 2 * lp_sm_count() / (tiles * H)));
+    dim3 grid(tiles, H, vparts);
+    const size_t smem = (size_t)TOK_TILE * (rank + shares) * sizeof(float);
 #define LP_LAUNCH_EXPAND(TW, TOut)                                                                                \
     do {                                                                                                          \
         if (grant_shared(latent_expand_kernel<TW, TOut>, smem, "latent_expand")) return -1;                       \
@@ -412,4 +492,30 @@ extern "C" int lp_latent_expand(const float* part, int shares, const void* uv, i
     else LP_REFUSE("latent_expand: dtype codes w=%d out=%d", w_dtype, out_dtype);
 #undef LP_LAUNCH_EXPAND
     return lp_check_launch("latent_expand");
+}
+
+// kv: bfloat16 [T, H * dn + H * dv] (every head's unrotated keys, then every head's values); shared_part: bfloat16
+// [T, dr]; pages: bfloat16 [num_pages, 2, H, page_size, dn + dr]; table: [B, pt_stride]; kv_len [B]: the sequences'
+// lengths, all of whose positions are in this step.
+extern "C" int lp_latent_heads_to_pages(const void* kv, const void* shared_part, const int* positions, const int* seq_ids,
+                                        const int* table, int pt_stride, const int* kv_len, void* pages, int T, int H,
+                                        int dn, int dr, int dv, int page_size, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || dn < 0 || dr < 0 || dv <= 0 || dv > dn + dr) LP_REFUSE("latent_heads_to_pages: %d heads of %d + %d, values of %d", H, dn, dr, dv);
+    if (page_size <= 0) LP_REFUSE("latent_heads_to_pages: page size %d", page_size);
+    lp_launch(latent_heads_to_pages_kernel, T, 256, 0, stream, (const __nv_bfloat16*)kv, (const __nv_bfloat16*)shared_part,
+              positions, seq_ids, table, pt_stride, kv_len, (__nv_bfloat16*)pages, H, dn, dr, dv, page_size);
+    return lp_check_launch("latent_heads_to_pages");
+}
+
+extern "C" int lp_latent_gate_heads(const void* heads, const float* gate, int ldg, void* out, int T, int H, int hd, int dv,
+                                    cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || dv <= 0 || dv > hd) LP_REFUSE("latent_gate_heads: %d heads of %d, values of %d", H, hd, dv);
+    const long long n = (long long)T * H * dv;
+    long long blocks = (n + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    lp_launch(latent_gate_heads_kernel, (unsigned)blocks, 256, 0, stream, (const __nv_bfloat16*)heads, gate, ldg,
+              (__nv_bfloat16*)out, T, H, hd, dv);
+    return lp_check_launch("latent_gate_heads");
 }

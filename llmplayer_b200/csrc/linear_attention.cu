@@ -4,7 +4,7 @@
 //     o_t = S_t^T q_t
 //
 // with a_t = sigmoid(z_t)^(1/tau) and z_t = A2 (A1 h_t) + bias (a low-rank map of the layer's input).
-// The state is float32, one block [H, dk, dv] per sequence, read at the start of a step and written
+// The state is float32, one block per sequence (stored [H, dv, dk]), read at the start of a step and written
 // back at its end; decays, their logarithms and every sum are float32.
 //
 //   lp_gla_decay    a[t, c] = exp(-softplus(-z[t, c]) / tau), z from the low-rank factor's output
@@ -38,15 +38,14 @@ gla_decay_kernel(const float* __restrict__ low, int ldl, const TW* __restrict__ 
 }
 
 // ---------------------------------------------------------------- scan
-// One CTA per (block of VT value columns, head, sequence); thread (j, part) keeps the state rows
-// part, part + KP, part + 2 KP, ... of value column j in registers. Tokens are brought to shared memory
-// TB at a time; per token every thread decays and updates its rows, forms its share of o_t[j], and the KP
-// shares meet in two shuffles.
-constexpr int KP = 4;             // threads that share a value column
-constexpr int VT = 64;            // value columns per CTA
+// One CTA per (block of VT value columns, head, sequence); KP threads share a value column j, thread (j, part)
+// keeping the state entries of key channels part, part + KP, part + 2 KP, ... of that column in registers.
+// Tokens are brought to shared memory TB at a time; per token every thread decays and updates its entries,
+// forms its share of o_t[j], and the KP shares meet in log2(KP) shuffles. The state is stored per head as
+// [dv, dk] (a column's channels lie together), so that the threads of a column read and write whole sectors.
 constexpr int TB = 16;            // tokens per round of loads
 
-template <int KPT>
+template <int KP, int VT, int KPT>
 __global__ void __launch_bounds__(VT * KP)
 gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off, const float* __restrict__ decay,
                 float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ q_start,
@@ -59,16 +58,16 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
     lp_grid_release();
     lp_grid_wait();
     const int h = blockIdx.y, b = blockIdx.z;
-    const int tid = threadIdx.x, part = tid & (KP - 1), jl = tid >> 2;
+    const int tid = threadIdx.x, part = tid % KP, jl = tid / KP;
     const int j = blockIdx.x * VT + jl;
     const bool live = j < dv;
     const int t0 = q_start[b], t1 = q_start[b + 1];
-    float* S = state + ((long long)slots[b] * H + h) * dk * dv;
+    float* S = state + (((long long)slots[b] * H + h) * dv + (live ? j : 0)) * dk;
     float s[KPT];
 #pragma unroll
     for (int i = 0; i < KPT; ++i) {
         const int c = part + KP * i;
-        s[i] = (live && c < dk) ? S[(long long)c * dv + j] : 0.f;
+        s[i] = (live && c < dk) ? S[c] : 0.f;
     }
     for (int tb = t0; tb < t1; tb += TB) {
         const int nt = min(TB, t1 - tb);
@@ -86,29 +85,43 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
             vs[e] = col < dv ? proj[(long long)(tb + i) * ld + v_off + h * dv + col] : 0.f;
         }
         __syncthreads();
-        for (int i = 0; i < nt; ++i) {
-            const float v = vs[i * VT + jl];
-            const float* qi = qs + i * dk;
-            const float* ki = ks + i * dk;
-            const float* ai = as + i * dk;
-            float acc = 0.f;
+        // the state runs through the tokens in order; each token's share of o_t[j] is kept, and the shares of all
+        // tokens of the round meet afterwards (shuffles that do not wait on one another)
+        float share[TB];
 #pragma unroll
-            for (int u = 0; u < KPT; ++u) {
-                const int c = part + KP * u;
-                if (c < dk) {
-                    s[u] = fmaf(ai[c], s[u], ki[c] * v);
-                    acc = fmaf(s[u], qi[c], acc);
+        for (int i = 0; i < TB; ++i) {
+            share[i] = 0.f;
+            if (i < nt) {
+                const float v = vs[i * VT + jl];
+                const float* qi = qs + i * dk;
+                const float* ki = ks + i * dk;
+                const float* ai = as + i * dk;
+                float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+                for (int u = 0; u < KPT; ++u) {
+                    const int c = part + KP * u;
+                    if (c < dk) {
+                        s[u] = fmaf(ai[c], s[u], ki[c] * v);
+                        if (u & 1) acc1 = fmaf(s[u], qi[c], acc1);
+                        else acc0 = fmaf(s[u], qi[c], acc0);
+                    }
                 }
+                share[i] = acc0 + acc1;
             }
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            if (part == 0 && live) out[((long long)(tb + i) * H + h) * dv + j] = acc;
         }
+#pragma unroll
+        for (int o = 1; o < KP; o <<= 1) {
+#pragma unroll
+            for (int i = 0; i < TB; ++i) share[i] += __shfl_xor_sync(0xffffffffu, share[i], o);
+        }
+#pragma unroll
+        for (int i = 0; i < TB; ++i)
+            if (i < nt && part == (i % KP) && live) out[((long long)(tb + i) * H + h) * dv + j] = share[i];
     }
 #pragma unroll
     for (int i = 0; i < KPT; ++i) {
         const int c = part + KP * i;
-        if (live && c < dk) S[(long long)c * dv + j] = s[i];
+        if (live && c < dk) S[c] = s[i];
     }
 }
 
@@ -157,7 +170,7 @@ extern "C" int lp_gla_decay(const float* low, int ldl, const void* a2, int w_dty
 }
 
 // proj: float32 [T, ld] with queries at q_off ([H, dk]), keys at k_off ([H, dk]), values at v_off ([H, dv]);
-// decay: float32 [T, H * dk]; state: float32 [slots, H, dk, dv]; out: float32 [T, H, dv].
+// decay: float32 [T, H * dk]; state: float32 [slots, H, dv, dk]; out: float32 [T, H, dv].
 extern "C" int lp_gla_scan(const float* proj, int ld, int q_off, int k_off, int v_off, const float* decay, float* state,
                            const int* slots, const int* q_start, float* out, int B, int H, int dk, int dv,
                            float q_scale, cudaStream_t stream) {
@@ -166,24 +179,25 @@ extern "C" int lp_gla_scan(const float* proj, int ld, int q_off, int k_off, int 
     if (dk > 512) LP_REFUSE("gla_scan: %d key channels per head (supported: up to 512)", dk);
     if (q_off < 0 || k_off < 0 || v_off < 0 || q_off + H * dk > ld || k_off + H * dk > ld || v_off + H * dv > ld)
         LP_REFUSE("gla_scan: slices at %d, %d, %d do not fit rows of %d", q_off, k_off, v_off, ld);
-    dim3 grid((dv + VT - 1) / VT, H, B);
-    const size_t smem = ((size_t)3 * TB * dk + (size_t)TB * VT) * sizeof(float);
-    const int kpt = (dk + KP - 1) / KP;
-#define LP_LAUNCH_SCAN(N)                                                                                             \
-    lp_launch(gla_scan_kernel<N>, grid, VT * KP, smem, stream, proj, ld, q_off, k_off, v_off, decay, state, slots,     \
-              q_start, out, H, dk, dv, q_scale)
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaSuccess;
-        if (kpt <= 64) e = cudaFuncSetAttribute(gla_scan_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        else e = cudaFuncSetAttribute(gla_scan_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) LP_REFUSE("gla_scan: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    }
-    if (kpt <= 4) LP_LAUNCH_SCAN(4);
-    else if (kpt <= 8) LP_LAUNCH_SCAN(8);
-    else if (kpt <= 16) LP_LAUNCH_SCAN(16);
-    else if (kpt <= 32) LP_LAUNCH_SCAN(32);
-    else if (kpt <= 64) LP_LAUNCH_SCAN(64);
-    else LP_LAUNCH_SCAN(128);
+#define LP_LAUNCH_SCAN(KP_, VT_, N)                                                                                   \
+    do {                                                                                                              \
+        dim3 grid((dv + VT_ - 1) / VT_, H, B);                                                                        \
+        const size_t smem = ((size_t)3 * TB * dk + (size_t)TB * VT_) * sizeof(float);                                 \
+        if (smem > 48 * 1024) {                                                                                       \
+            cudaError_t e = cudaFuncSetAttribute(gla_scan_kernel<KP_, VT_, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) LP_REFUSE("gla_scan: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e)); \
+        }                                                                                                             \
+        lp_launch(gla_scan_kernel<KP_, VT_, N>, grid, VT_ * KP_, smem, stream, proj, ld, q_off, k_off, v_off, decay,   \
+                  state, slots, q_start, out, H, dk, dv, q_scale);                                                    \
+    } while (0)
+    // few key channels: 4 threads per column, 64 columns per CTA; from 32 channels on: 16 threads per column, 16 columns
+    if (dk <= 8) LP_LAUNCH_SCAN(4, 64, 2);
+    else if (dk <= 16) LP_LAUNCH_SCAN(4, 64, 4);
+    else if (dk < 32) LP_LAUNCH_SCAN(4, 64, 8);
+    else if (dk <= 64) LP_LAUNCH_SCAN(16, 16, 4);
+    else if (dk <= 128) LP_LAUNCH_SCAN(16, 16, 8);
+    else if (dk <= 256) LP_LAUNCH_SCAN(16, 16, 16);
+    else LP_LAUNCH_SCAN(16, 16, 32);
 #undef LP_LAUNCH_SCAN
     return lp_check_launch("gla_scan");
 }

@@ -58,7 +58,10 @@ _SIGNATURES = {
                                     _P, _P],
     },
     "latent_attention": {
-        "lp_latent_prepare": [_P, _I, _I, _I, _P, _F, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+        "lp_latent_prepare": [_P, _I, _I, _I, _P, _F, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P,
+                              _P],
+        "lp_latent_heads_to_pages": [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+        "lp_latent_gate_heads": [_P, _P, _I, _P, _I, _I, _I, _I, _P],
         "lp_latent_absorb": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _P],
         "lp_latent_attend_rows": [],
         "lp_latent_attend": [_P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
@@ -998,11 +1001,15 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, page
 # --------------------------------------------------------------------------- latent attention
 def latent_prepare(proj: torch.Tensor, q_off: int, kv_off: int, gain: torch.Tensor, eps: float, rotation: Rotation,
                    positions: torch.Tensor, seq_ids: torch.Tensor, page_table: torch.Tensor, q_out: torch.Tensor,
-                   pages: torch.Tensor, *, num_heads: int, nope_dim: int, rope_dim: int, kv_rank: int) -> None:
+                   pages: torch.Tensor, *, num_heads: int, nope_dim: int, rope_dim: int, kv_rank: int,
+                   latent_out: Optional[torch.Tensor] = None, shared_out: Optional[torch.Tensor] = None,
+                   q_half: Optional[torch.Tensor] = None) -> None:
     """From the float32 projection ``proj`` [T, F] (queries at column ``q_off``, [H, nope + rope]; latent and
     shared key part at ``kv_off``, [rank + rope]): RMS-norm the latent with ``gain``, rotate the shared key
     part and write both into ``pages`` [num_pages, page_size, rank + rope] at the tokens' positions; rotate the
-    queries' rope parts and write the queries to ``q_out`` float32 [T, H, nope + rope]."""
+    queries' rope parts and write the queries to ``q_out`` float32 [T, H, nope + rope]. Optional bfloat16 copies
+    that lie together, for a step that forms every head's keys and values outright: ``latent_out`` [T, rank],
+    ``shared_out`` [T, rope], ``q_half`` [T, H * (nope + rope)]."""
     _want(proj, "latent_prepare proj", torch.float32, 2)
     _want(gain, "latent_prepare gain", torch.float32, 1)
     _want(positions, "latent_prepare positions", torch.int32, 1)
@@ -1016,6 +1023,12 @@ def latent_prepare(proj: torch.Tensor, q_off: int, kv_off: int, gain: torch.Tens
             or positions.numel() != T or seq_ids.numel() != T):
         raise KernelError(f"latent_prepare: proj {tuple(proj.shape)}, q_out {tuple(q_out.shape)}, pages "
                           f"{tuple(pages.shape)} for {H} heads of {dn} + {dr} over rank {rank}")
+    for extra, shape, what in ((latent_out, (T, rank), "latent_out"), (shared_out, (T, dr), "shared_out"),
+                               (q_half, (T, H * (dn + dr)), "q_half")):
+        if extra is not None:
+            _want(extra, f"latent_prepare {what}", torch.bfloat16, 2)
+            if extra.shape != shape:
+                raise KernelError(f"latent_prepare: {what} {tuple(extra.shape)}, expected {shape}")
     freq_ptr, rot, interleaved = rotation.checked("latent_prepare")
     if interleaved:
         raise KernelError("latent_prepare: pairs of neighbours are not supported, only (i, i + half)")
@@ -1023,7 +1036,52 @@ def latent_prepare(proj: torch.Tensor, q_off: int, kv_off: int, gain: torch.Tens
     _check(lib, lib.lp_latent_prepare(
         proj.data_ptr(), proj.shape[1], int(q_off), int(kv_off), gain.data_ptr(), float(eps), freq_ptr, rot,
         positions.data_ptr(), seq_ids.data_ptr(), page_table.data_ptr(), page_table.shape[1], q_out.data_ptr(),
-        pages.data_ptr(), _code(pages, "latent_prepare pages"), T, H, dn, dr, rank, pages.shape[1], _stream()))
+        pages.data_ptr(), _code(pages, "latent_prepare pages"), T, H, dn, dr, rank, pages.shape[1], _ptr(latent_out),
+        _ptr(shared_out), _ptr(q_half), _stream()))
+
+
+def latent_heads_to_pages(kv: torch.Tensor, shared_part: torch.Tensor, positions: torch.Tensor, seq_ids: torch.Tensor,
+                          table: torch.Tensor, kv_len: torch.Tensor, pages: torch.Tensor, *, num_heads: int, nope_dim: int,
+                          rope_dim: int, value_dim: int) -> None:
+    """Lay the heads' keys and values of a step's tokens out as pages of ordinary keys and values
+    [num_pages, 2, H, page_size, nope + rope]: key of head h = [kv[t, h * nope + :] | shared_part[t]], value of
+    head h = kv[t, H * nope + h * dv + :] padded with zeros. All bfloat16; ``table`` [B, W] names the pages. The step
+    holds every position of its sequences (``kv_len`` [B]); the rest of each sequence's last page is cleared."""
+    H, dn, dr, dv = num_heads, nope_dim, rope_dim, value_dim
+    _want(kv, "latent_heads_to_pages kv", torch.bfloat16, 2)
+    _want(shared_part, "latent_heads_to_pages shared part", torch.bfloat16, 2)
+    _want(pages, "latent_heads_to_pages pages", torch.bfloat16, 5)
+    _want(table, "latent_heads_to_pages table", torch.int32, 2)
+    _want(kv_len, "latent_heads_to_pages kv_len", torch.int32, 1)
+    T = kv.shape[0]
+    if (kv.shape[1] != H * (dn + dv) or shared_part.shape != (T, dr) or pages.shape[1] != 2 or pages.shape[2] != H
+            or pages.shape[4] != dn + dr or positions.numel() != T or seq_ids.numel() != T):
+        raise KernelError(f"latent_heads_to_pages: kv {tuple(kv.shape)}, shared part {tuple(shared_part.shape)}, pages "
+                          f"{tuple(pages.shape)}")
+    lib = library("latent_attention")
+    _check(lib, lib.lp_latent_heads_to_pages(kv.data_ptr(), shared_part.data_ptr(), positions.data_ptr(), seq_ids.data_ptr(),
+                                             table.data_ptr(), table.shape[1], kv_len.data_ptr(), pages.data_ptr(), T, H, dn, dr, dv,
+                                             pages.shape[3], _stream()))
+
+
+def latent_gate_heads(heads: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, *, num_heads: int,
+                      head_dim: int, value_dim: int) -> torch.Tensor:
+    """out[t, h * dv + v] = heads[t, h * hd + v] * sigmoid(gate[t, h]) (bfloat16; ``gate`` float32 [T, H], may be a
+    column slice, or None)."""
+    _want(heads, "latent_gate_heads heads", torch.bfloat16, 2)
+    _want(out, "latent_gate_heads out", torch.bfloat16, 2)
+    T = heads.shape[0]
+    if heads.shape[1] != num_heads * head_dim or out.shape != (T, num_heads * value_dim):
+        raise KernelError(f"latent_gate_heads: heads {tuple(heads.shape)}, out {tuple(out.shape)}")
+    gp, ldg = (None, 0)
+    if gate is not None:
+        gp, ldg = _slice(gate, "latent_gate_heads gate")
+        if gate.shape != (T, num_heads):
+            raise KernelError(f"latent_gate_heads: gate {tuple(gate.shape)} for {T} tokens and {num_heads} heads")
+    lib = library("latent_attention")
+    _check(lib, lib.lp_latent_gate_heads(heads.data_ptr(), gp, ldg, out.data_ptr(), T, num_heads, head_dim, value_dim,
+                                         _stream()))
+    return out
 
 
 def latent_absorb(q: torch.Tensor, k_up: torch.Tensor, out: torch.Tensor, *, nope_dim: int, rope_dim: int) -> torch.Tensor:
@@ -1044,10 +1102,10 @@ def latent_absorb(q: torch.Tensor, k_up: torch.Tensor, out: torch.Tensor, *, nop
 
 def latent_shares(batch: int, max_new: int, num_heads: int, table_width: int, page_size: int) -> int:
     """Into how many shares :func:`latent_attend` cuts a sequence's keys: one while the (token, head) rows
-    alone fill the SMs, else as many as leave each share at least four pages."""
+    alone fill the SMs, else as many as the SMs have room for, down to shares of one block of 32 keys."""
     rows = library("latent_attention").lp_latent_attend_rows()
     ctas = batch * -(-max_new * num_heads // rows)
-    return max(1, min(num_sms() // max(ctas, 1), table_width // 4))
+    return max(1, min(num_sms() // max(ctas, 1), table_width * (page_size // 32)))
 
 
 def latent_attend(q_abs: torch.Tensor, pages: torch.Tensor, page_table: torch.Tensor, q_start: torch.Tensor,
@@ -1123,7 +1181,8 @@ def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torc
              slots: torch.Tensor, q_start: torch.Tensor, out: torch.Tensor, *, num_heads: int, key_dim: int,
              value_dim: int, q_scale: float) -> torch.Tensor:
     """The recurrence S <- diag(decay_t) S + k_t v_t^T, out_t = S^T (q_t * q_scale) over the step's tokens of every
-    sequence, from and into ``state`` float32 [slots, H, dk, dv] (row ``slots[b]`` for sequence b). ``proj``: float32
+    sequence, from and into ``state`` float32 [slots, H, dv, dk] (row ``slots[b]`` for sequence b; a value column's
+    key channels lie together). ``proj``: float32
     [T, F] with queries, keys and values at the given columns; ``decay``: float32 [T, H * dk]; ``out``: float32 [T, H * dv]."""
     _want(proj, "gla_scan proj", torch.float32, 2)
     _want(decay, "gla_scan decay", torch.float32, 2)
@@ -1134,7 +1193,7 @@ def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torc
     T = proj.shape[0]
     H, dk, dv = num_heads, key_dim, value_dim
     B = slots.numel()
-    if (decay.shape != (T, H * dk) or state.shape[1:] != (H, dk, dv) or out.shape != (T, H * dv)
+    if (decay.shape != (T, H * dk) or state.shape[1:] != (H, dv, dk) or out.shape != (T, H * dv)
             or q_start.numel() != B + 1):
         raise KernelError(f"gla_scan: proj {tuple(proj.shape)}, decay {tuple(decay.shape)}, state {tuple(state.shape)}, "
                           f"out {tuple(out.shape)}, {B} sequences")

@@ -5,7 +5,9 @@ Each position keeps one row: the RMS-normed latent c (``kv_rank`` values) and on
 v_up[h] c; its query is [nope_dim unrotated | rope_dim rotated]. The kernels apply k_up to the query
 instead of to every cached latent, attend over the cached rows with all heads at once, and apply v_up to
 the weighted sum of latents (csrc/latent_attention.cu). An optional output gate scales head h's output by
-sigmoid(out_gate[h] . x).
+sigmoid(out_gate[h] . x). A step of prompts that start at their first token, in bfloat16, instead forms every
+head's keys and values from the latents in one product and runs the tensor-core attention of ordinary heads
+over them; the cache is written the same either way.
 
 The part offers its input projections to the block (``input_projections``), so that a block whose
 sublayers all read one normed input can form them in one product, and takes the product's float32 sums
@@ -63,6 +65,8 @@ class LatentAttention(Part):
         self._inputs = [tensors[s.q], tensors[s.kv_down]] + ([tensors[s.out_gate]] if s.out_gate is not None else [])
         self.k_up = runtime.matrix(tensors[s.k_up])
         self.v_up = runtime.matrix(tensors[s.v_up])
+        self._k_up_host, self._v_up_host = tensors[s.k_up], tensors[s.v_up]
+        self._up = None                     # both maps stacked, for steps that form every head's keys and values
         self.latent_gain = runtime.gain(tensors[s.latent_norm])
         self.out = Linear([tensors[s.o]], runtime)
         self.position.load(tensors, runtime)
@@ -93,6 +97,8 @@ class LatentAttention(Part):
             raise ConfigError("latent attention takes position encodings that are rotations")
         table = ctx.page_tables[cache.group_index]
         q = ctx.buffer("latent_q", (T, H, dn + dr), torch.float32)
+        if self._forms_heads(ctx, cache):
+            return self._forward_heads(ctx, cache, proj, q_off, kv_off, gate_off, rotation, table, q, out)
         with ops.section("attention.position"):
             ops.latent_prepare(proj, q_off, kv_off, self.latent_gain, s.norm_eps, rotation, ctx.positions, ctx.seq_ids,
                                table, q, cache.pages, num_heads=H, nope_dim=dn, rope_dim=dr, kv_rank=rank)
@@ -108,6 +114,61 @@ class LatentAttention(Part):
         gate = proj[:, gate_off:gate_off + H] if s.out_gate is not None else None
         with ops.section("attention.values"):
             ops.latent_expand(partials, self.v_up, gate, o, value_dim=dv)
+        with ops.section("attention.out"):
+            self.out.store(o, out, ctx)
+        return out
+
+    # ------------------------------------------------------------------ prompts: every head's keys and values outright
+    HEADS_MIN_TOKENS = 48
+
+    def _forms_heads(self, ctx, cache) -> bool:
+        """Whether this step forms every head's keys and values and runs the tensor-core attention of ordinary
+        heads over them: the bfloat16 path, every sequence at its first token (nothing cached to attend over),
+        enough tokens for it to pay, and head sizes that kernel takes."""
+        s, rt = self.spec, self.runtime
+        hd = s.nope_dim + s.rope_dim
+        return (rt.fast and cache.pages.dtype == torch.bfloat16 and ctx.max_new >= self.HEADS_MIN_TOKENS
+                and all(p == 0 for p in ctx.first_positions) and hd % 16 == 0 and hd <= 256 and s.value_dim <= hd
+                and s.kv_rank % 8 == 0)
+
+    def _forward_heads(self, ctx, cache, proj, q_off, kv_off, gate_off, rotation, table, q, out):
+        s = self.spec
+        T = proj.shape[0]
+        H, dn, dr, dv, rank = s.num_heads, s.nope_dim, s.rope_dim, s.value_dim, s.kv_rank
+        hd = dn + dr
+        page = cache.pages.shape[1]
+        latent = ctx.buffer("latent_rows", (T, rank), torch.bfloat16)
+        shared = ctx.buffer("latent_shared_key", (T, dr), torch.bfloat16)
+        q_half = ctx.buffer("q", (T, H * hd), torch.bfloat16)
+        with ops.section("attention.position"):
+            ops.latent_prepare(proj, q_off, kv_off, self.latent_gain, s.norm_eps, rotation, ctx.positions, ctx.seq_ids,
+                               table, q, cache.pages, num_heads=H, nope_dim=dn, rope_dim=dr, kv_rank=rank,
+                               latent_out=latent, shared_out=shared, q_half=q_half)
+        if self._up is None:
+            self._up = Linear([self._k_up_host, self._v_up_host], self.runtime)
+        kv = ctx.buffer("latent_heads", (T, H * (dn + dv)), torch.bfloat16)
+        with ops.section("attention.heads"):
+            self._up.store(latent, kv, ctx)
+        # pages of this step only: sequence after sequence, each from a page of its own
+        counts = [-(-n // page) for n in ctx.new_counts]
+        width = max(counts)
+        rows, base = [], 0
+        for c in counts:
+            rows.append([base + i for i in range(c)] + [0] * (width - c))
+            base += c
+        step_table = torch.tensor(rows, dtype=torch.int32).to(proj.device, non_blocking=True)
+        step_pages = ctx.buffer("latent_head_pages", (base, 2, H, page, hd), torch.bfloat16)
+        with ops.section("attention.heads"):
+            ops.latent_heads_to_pages(kv, shared, ctx.positions, ctx.seq_ids, step_table, ctx.kv_len, step_pages, num_heads=H,
+                                      nope_dim=dn, rope_dim=dr, value_dim=dv)
+        heads = ctx.buffer("latent_head_out", (T, H * hd), torch.bfloat16)
+        with ops.section("attention.scores"):
+            ops.attention_prefill(q_half, heads, step_pages, step_table, ctx.q_start, ctx.kv_len, ctx.max_new, num_heads=H,
+                                  num_kv_heads=H, head_dim=hd, scale=s.scale, window=None)
+        o = ctx.buffer("attn_out", (T, H * dv), torch.bfloat16)
+        gate = proj[:, gate_off:gate_off + H] if s.out_gate is not None else None
+        with ops.section("attention.values"):
+            ops.latent_gate_heads(heads, gate, o, num_heads=H, head_dim=hd, value_dim=dv)
         with ops.section("attention.out"):
             self.out.store(o, out, ctx)
         return out

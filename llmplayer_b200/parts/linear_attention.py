@@ -4,7 +4,7 @@
     a_t = sigmoid(up(down(x_t)) + bias)^(1 / temperature)
 
 Each head's o_t is RMS-normed over its values with one gain shared by the heads, multiplied by
-silu(gate x_t), and the heads are projected by ``o``. The state [heads, key_dim, value_dim] starts at zero
+silu(gate x_t), and the heads are projected by ``o``. The state (kept as [heads, value_dim, key_dim]) starts at zero
 (the cache zeroes a slot's row when it is taken) and is carried from step to step; the kernels read the
 row of each sequence's slot from the device, so one-token steps replay from captured graphs
 (csrc/linear_attention.cu).
@@ -70,7 +70,7 @@ class GatedLinearAttention(Part):
     # ------------------------------------------------------------------ cache
     def cache_request(self):
         s = self.spec
-        return StateRequest((s.num_heads, s.key_dim, s.value_dim), torch.float32)
+        return StateRequest((s.num_heads, s.value_dim, s.key_dim), torch.float32)     # stored [head, value column, key channel]
 
     # ------------------------------------------------------------------ step
     def input_projections(self) -> List[torch.Tensor]:

@@ -84,7 +84,7 @@ def test_cache_groups_rows_and_states():
     from llmplayer_b200.engine.model import Model
     model = Model(config_from_dict(WIDE).layout())
     requests = model.cache_requests()
-    assert requests == [StateRequest((2, 64, 128), torch.float32), RowsRequest(192), RowsRequest(32)]
+    assert requests == [StateRequest((2, 128, 64), torch.float32), RowsRequest(192), RowsRequest(32)]
     cache = SequenceCache(requests, max_tokens=256, max_slots=3, kv_dtype=torch.bfloat16, device="cpu")
     assert [tuple(g.storage.shape) for g in cache.groups] == [(1, 4, 64, 192), (1, 4, 64, 32)]
     a = cache.acquire()
