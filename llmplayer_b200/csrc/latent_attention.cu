@@ -161,6 +161,7 @@ latent_absorb_kernel(const float* __restrict__ q, const TW* __restrict__ uk, flo
         float acc[TOK_TILE];
 #pragma unroll
         for (int i = 0; i < TOK_TILE; ++i) acc[i] = 0.f;
+#pragma unroll 8
         for (int d = 0; d < dn; ++d) {
             const float w = lp_to_float(u[(long long)d * rank + r]);
 #pragma unroll
@@ -189,9 +190,13 @@ latent_attend_kernel(const float* __restrict__ qa, const TKV* __restrict__ pages
                      float* __restrict__ part, int H, int rank, int dr, int page_size, float scale, int shares) {
     extern __shared__ float smem[];
     constexpr int ROWS = WARPS * RW;
-    const int Dk = rank + dr, KS = Dk + 1;
+    // rows of a multiple of 4 values are read four at a time (a key row's stride of Dk + 4 floats keeps the lanes'
+    // 16-byte reads on distinct banks); other widths one value at a time with a stride of Dk + 1
+    const int Dk = rank + dr;
+    const bool vec = (Dk & 3) == 0;
+    const int KS = vec ? Dk + 4 : Dk + 1;
     float* Qs = smem;                       // [ROWS][Dk]
-    float* Ks = smem + ROWS * Dk;           // [KEYS][Dk + 1]
+    float* Ks = smem + ROWS * Dk;           // [KEYS][KS]
     lp_grid_release();
     lp_grid_wait();
     const int b = blockIdx.y, share = blockIdx.z;
@@ -204,9 +209,9 @@ latent_attend_kernel(const float* __restrict__ qa, const TKV* __restrict__ pages
     const int n_rows = min(ROWS, rows_total - r0);
     const int first_pos = len - n_new;                    // position of the sequence's first new token
     // queries of this CTA
-    for (int e = tid; e < ROWS * Dk; e += blockDim.x) {
-        const int r = e / Dk;
-        Qs[e] = r < n_rows ? qa[((long long)first_tok * H + r0) * Dk + e] : 0.f;
+    for (int r = warp; r < ROWS; r += WARPS) {
+        const float* src = qa + ((long long)first_tok * H + r0 + r) * Dk;
+        for (int e = lane; e < Dk; e += 32) Qs[r * Dk + e] = r < n_rows ? src[e] : 0.f;
     }
     int pos_r[RW];
     float m[RW], l[RW], o[RW][NC];
@@ -248,10 +253,25 @@ latent_attend_kernel(const float* __restrict__ qa, const TKV* __restrict__ pages
         for (int r = 0; r < RW; ++r) dot[r] = 0.f;
         const float* kr = Ks + lane * KS;
         const float* qw = Qs + warp * RW * Dk;
-        for (int d = 0; d < Dk; ++d) {
-            const float kv = kr[d];
+        if (vec) {
+#pragma unroll 2
+            for (int d = 0; d < Dk; d += 4) {
+                const float4 kv = *reinterpret_cast<const float4*>(kr + d);
 #pragma unroll
-            for (int r = 0; r < RW; ++r) dot[r] = fmaf(qw[r * Dk + d], kv, dot[r]);
+                for (int r = 0; r < RW; ++r) {
+                    const float4 qv = *reinterpret_cast<const float4*>(qw + r * Dk + d);
+                    dot[r] = fmaf(qv.x, kv.x, dot[r]);
+                    dot[r] = fmaf(qv.y, kv.y, dot[r]);
+                    dot[r] = fmaf(qv.z, kv.z, dot[r]);
+                    dot[r] = fmaf(qv.w, kv.w, dot[r]);
+                }
+            }
+        } else {
+            for (int d = 0; d < Dk; ++d) {
+                const float kv = kr[d];
+#pragma unroll
+                for (int r = 0; r < RW; ++r) dot[r] = fmaf(qw[r * Dk + d], kv, dot[r]);
+            }
         }
         float p[RW];
 #pragma unroll
@@ -300,6 +320,46 @@ latent_attend_kernel(const float* __restrict__ qa, const TKV* __restrict__ pages
             dst[rank] = m[r];
             dst[rank + 1] = l[r];
         }
+    }
+}
+
+// ---------------------------------------------------------------- merge
+// The shares of one (token, head) row become one: out = [sum_s o_s e^(m_s - M) / sum_s l_s e^(m_s - M) | 0 | 1],
+// the form of a single share whose sum of weights is one. One CTA per row; every warp forms the weights.
+__global__ void __launch_bounds__(128)
+latent_merge_kernel(const float* __restrict__ part, int shares, float* __restrict__ out, int rank) {
+    extern __shared__ float ws[];                         // [shares]
+    lp_grid_release();
+    lp_grid_wait();
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int width = rank + 2;
+    const float* p = part + (long long)blockIdx.x * shares * width;
+    float M = -INFINITY;
+    for (int s = lane; s < shares; s += 32) M = fmaxf(M, p[s * width + rank]);
+    M = lp_warp_max(M);
+    float L = 0.f;
+    for (int s = lane; s < shares; s += 32) {
+        const float ms = p[s * width + rank];
+        L += ms == -INFINITY ? 0.f : p[s * width + rank + 1] * expf(ms - M);
+    }
+    L = lp_warp_sum(L);
+    const float inv = 1.0f / L;
+    if (tid < 32)
+        for (int s = lane; s < shares; s += 32) {
+            const float ms = p[s * width + rank];
+            ws[s] = ms == -INFINITY ? 0.f : expf(ms - M) * inv;
+        }
+    __syncthreads();
+    float* dst = out + (long long)blockIdx.x * width;
+    for (int r = tid; r < rank; r += blockDim.x) {
+        float acc = 0.f;
+#pragma unroll 8
+        for (int s = 0; s < shares; ++s) acc = fmaf(p[(long long)s * width + r], ws[s], acc);
+        dst[r] = acc;
+    }
+    if (tid == 0) {
+        dst[rank] = 0.f;
+        dst[rank + 1] = 1.f;
     }
 }
 
@@ -442,7 +502,7 @@ extern "C" int lp_latent_attend(const float* qa, const void* pages, int kv_dtype
     if (shares <= 0 || shares > 65535 || B > 65535) LP_REFUSE("latent_attend: %d shares, %d sequences", shares, B);
     constexpr int ROWS = WARPS * ATTEND_RW;
     const int Dk = rank + dr;
-    const size_t smem = ((size_t)ROWS * Dk + (size_t)KEYS * (Dk + 1)) * sizeof(float);
+    const size_t smem = ((size_t)ROWS * Dk + (size_t)KEYS * (Dk + 4)) * sizeof(float);
     if (smem > 227 * 1024) LP_REFUSE("latent_attend: rows of %d values need %zu bytes of shared memory", Dk, smem);
     dim3 grid((unsigned)(((long long)max_new * H + ROWS - 1) / ROWS), B, shares);
 #define LP_LAUNCH_ATTEND(TKV, NC)                                                                                    \
@@ -465,6 +525,14 @@ extern "C" int lp_latent_attend(const float* qa, const void* pages, int kv_dtype
 #undef LP_PICK_NC
 #undef LP_LAUNCH_ATTEND
     return lp_check_launch("latent_attend");
+}
+
+// part: float32 [rows, shares, rank + 2] as lp_latent_attend leaves it; out: float32 [rows, 1, rank + 2], one share.
+extern "C" int lp_latent_merge(const float* part, int shares, float* out, int rows, int rank, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (shares <= 0 || rank <= 0) LP_REFUSE("latent_merge: %d shares of rank %d", shares, rank);
+    lp_launch(latent_merge_kernel, rows, 128, (size_t)shares * sizeof(float), stream, part, shares, out, rank);
+    return lp_check_launch("latent_merge");
 }
 
 // part: as lp_latent_attend leaves it; uv: [H * dv, rank]; gate: float32 [T, ldg] with one value per head

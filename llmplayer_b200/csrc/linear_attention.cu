@@ -45,11 +45,22 @@ gla_decay_kernel(const float* __restrict__ low, int ldl, const TW* __restrict__ 
 // [dv, dk] (a column's channels lie together), so that the threads of a column read and write whole sectors.
 constexpr int TB = 16;            // tokens per round of loads
 
+//
+// Long prompts are cut into chunks of `chunk` tokens that run side by side (blockIdx.z = sequence * chunks + chunk):
+//   mode LOCAL    every chunk starts from zero, writes no output, and leaves its final state and the product of its
+//                 decays per channel in `chunk_state` / `chunk_decay`;
+//   (gla_combine_kernel then walks a sequence's chunks in order: start_(c+1) = decay_c * start_c + local_c, puts each
+//   chunk's start state where its local state was, and the last one into the sequence's state row)
+//   mode OUTPUT   every chunk starts from its start state and writes its outputs.
+// mode WHOLE is the recurrence in one pass, from and into the sequence's state row (decode steps, short prompts).
+constexpr int SCAN_WHOLE = 0, SCAN_LOCAL = 1, SCAN_OUTPUT = 2;
+
 template <int KP, int VT, int KPT>
 __global__ void __launch_bounds__(VT * KP)
 gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off, const float* __restrict__ decay,
                 float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ q_start,
-                float* __restrict__ out, int H, int dk, int dv, float q_scale) {
+                float* __restrict__ out, int H, int dk, int dv, float q_scale, int mode, int chunks, int chunk,
+                float* __restrict__ chunk_state, float* __restrict__ chunk_decay) {
     extern __shared__ float sm[];
     float* qs = sm;                         // [TB][dk]
     float* ks = qs + TB * dk;
@@ -57,17 +68,24 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
     float* vs = as + TB * dk;               // [TB][VT]
     lp_grid_release();
     lp_grid_wait();
-    const int h = blockIdx.y, b = blockIdx.z;
+    const int h = blockIdx.y, b = blockIdx.z / chunks, piece = blockIdx.z - b * chunks;
     const int tid = threadIdx.x, part = tid % KP, jl = tid / KP;
     const int j = blockIdx.x * VT + jl;
     const bool live = j < dv;
-    const int t0 = q_start[b], t1 = q_start[b + 1];
-    float* S = state + (((long long)slots[b] * H + h) * dv + (live ? j : 0)) * dk;
-    float s[KPT];
+    int t0 = q_start[b], t1 = q_start[b + 1];
+    if (mode != SCAN_WHOLE) {
+        t0 += piece * chunk;
+        t1 = min(t1, t0 + chunk);
+        if (t0 >= t1) return;                             // this sequence has fewer chunks
+    }
+    float* S = mode == SCAN_WHOLE ? state + (((long long)slots[b] * H + h) * dv + (live ? j : 0)) * dk
+                                  : chunk_state + (((long long)blockIdx.z * H + h) * dv + (live ? j : 0)) * dk;
+    float s[KPT], prod[KPT];
 #pragma unroll
     for (int i = 0; i < KPT; ++i) {
         const int c = part + KP * i;
-        s[i] = (live && c < dk) ? S[c] : 0.f;
+        s[i] = (mode != SCAN_LOCAL && live && c < dk) ? S[c] : 0.f;
+        prod[i] = 1.f;
     }
     for (int tb = t0; tb < t1; tb += TB) {
         const int nt = min(TB, t1 - tb);
@@ -102,6 +120,7 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
                     const int c = part + KP * u;
                     if (c < dk) {
                         s[u] = fmaf(ai[c], s[u], ki[c] * v);
+                        if (mode == SCAN_LOCAL) prod[u] *= ai[c];
                         if (u & 1) acc1 = fmaf(s[u], qi[c], acc1);
                         else acc0 = fmaf(s[u], qi[c], acc0);
                     }
@@ -115,14 +134,46 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
             for (int i = 0; i < TB; ++i) share[i] += __shfl_xor_sync(0xffffffffu, share[i], o);
         }
 #pragma unroll
-        for (int i = 0; i < TB; ++i)
-            if (i < nt && part == (i % KP) && live) out[((long long)(tb + i) * H + h) * dv + j] = share[i];
+        if (mode != SCAN_LOCAL) {
+#pragma unroll
+            for (int i = 0; i < TB; ++i)
+                if (i < nt && part == (i % KP) && live) out[((long long)(tb + i) * H + h) * dv + j] = share[i];
+        }
     }
+    if (mode == SCAN_OUTPUT) return;
 #pragma unroll
     for (int i = 0; i < KPT; ++i) {
         const int c = part + KP * i;
         if (live && c < dk) S[c] = s[i];
+        if (mode == SCAN_LOCAL && blockIdx.x == 0 && jl == 0 && c < dk)
+            chunk_decay[((long long)blockIdx.z * H + h) * dk + c] = prod[i];
     }
+}
+
+// One thread per state entry (sequence, head, value column, key channel) walks the sequence's chunks in order.
+__global__ void __launch_bounds__(256)
+gla_combine_kernel(float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ q_start,
+                   float* __restrict__ chunk_state, const float* __restrict__ chunk_decay, int H, int dk, int dv,
+                   int chunks, int chunk) {
+    lp_grid_release();
+    lp_grid_wait();
+    const int b = blockIdx.y;
+    const long long per = (long long)H * dv * dk;
+    const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= per) return;
+    const int h = (int)(e / ((long long)dv * dk));
+    const int c = (int)(e % dk);
+    const int n = q_start[b + 1] - q_start[b];
+    const int used = (n + chunk - 1) / chunk;
+    float* row = state + (long long)slots[b] * per + e;
+    float s = *row;
+    for (int p = 0; p < used; ++p) {
+        float* at = chunk_state + ((long long)b * chunks + p) * per + e;
+        const float local = *at;
+        *at = s;
+        s = fmaf(chunk_decay[(((long long)b * chunks + p) * H + h) * dk + c], s, local);
+    }
+    *row = s;
 }
 
 // ---------------------------------------------------------------- finish
@@ -171,24 +222,43 @@ extern "C" int lp_gla_decay(const float* low, int ldl, const void* a2, int w_dty
 
 // proj: float32 [T, ld] with queries at q_off ([H, dk]), keys at k_off ([H, dk]), values at v_off ([H, dv]);
 // decay: float32 [T, H * dk]; state: float32 [slots, H, dv, dk]; out: float32 [T, H, dv].
+// chunks > 1 (with chunk tokens each, chunk_state float32 [B, chunks, H, dv, dk], chunk_decay float32 [B, chunks, H, dk]):
+// the chunks of a sequence run side by side in three launches; every sequence needs at most `chunks` chunks.
 extern "C" int lp_gla_scan(const float* proj, int ld, int q_off, int k_off, int v_off, const float* decay, float* state,
                            const int* slots, const int* q_start, float* out, int B, int H, int dk, int dv,
-                           float q_scale, cudaStream_t stream) {
+                           float q_scale, int chunks, int chunk, float* chunk_state, float* chunk_decay,
+                           cudaStream_t stream) {
     if (B <= 0) return 0;
+    if (chunks < 1) chunks = 1;
+    if (chunks > 1 && (chunk <= 0 || !chunk_state || !chunk_decay)) LP_REFUSE("gla_scan: %d chunks without their buffers", chunks);
+    if ((long long)B * chunks > 65535) LP_REFUSE("gla_scan: %d sequences in %d chunks exceed the grid", B, chunks);
     if (H <= 0 || H > 65535 || B > 65535 || dk <= 0 || dv <= 0) LP_REFUSE("gla_scan: %d sequences, %d heads of %d x %d", B, H, dk, dv);
     if (dk > 512) LP_REFUSE("gla_scan: %d key channels per head (supported: up to 512)", dk);
     if (q_off < 0 || k_off < 0 || v_off < 0 || q_off + H * dk > ld || k_off + H * dk > ld || v_off + H * dv > ld)
         LP_REFUSE("gla_scan: slices at %d, %d, %d do not fit rows of %d", q_off, k_off, v_off, ld);
 #define LP_LAUNCH_SCAN(KP_, VT_, N)                                                                                   \
     do {                                                                                                              \
-        dim3 grid((dv + VT_ - 1) / VT_, H, B);                                                                        \
+        dim3 grid((dv + VT_ - 1) / VT_, H, B * chunks);                                                               \
         const size_t smem = ((size_t)3 * TB * dk + (size_t)TB * VT_) * sizeof(float);                                 \
         if (smem > 48 * 1024) {                                                                                       \
             cudaError_t e = cudaFuncSetAttribute(gla_scan_kernel<KP_, VT_, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) LP_REFUSE("gla_scan: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e)); \
         }                                                                                                             \
-        lp_launch(gla_scan_kernel<KP_, VT_, N>, grid, VT_ * KP_, smem, stream, proj, ld, q_off, k_off, v_off, decay,   \
-                  state, slots, q_start, out, H, dk, dv, q_scale);                                                    \
+        if (chunks == 1) {                                                                                            \
+            lp_launch(gla_scan_kernel<KP_, VT_, N>, grid, VT_ * KP_, smem, stream, proj, ld, q_off, k_off, v_off,     \
+                      decay, state, slots, q_start, out, H, dk, dv, q_scale, SCAN_WHOLE, 1, 0, (float*)nullptr,       \
+                      (float*)nullptr);                                                                               \
+        } else {                                                                                                      \
+            lp_launch(gla_scan_kernel<KP_, VT_, N>, grid, VT_ * KP_, smem, stream, proj, ld, q_off, k_off, v_off,     \
+                      decay, state, slots, q_start, out, H, dk, dv, q_scale, SCAN_LOCAL, chunks, chunk, chunk_state,  \
+                      chunk_decay);                                                                                   \
+            const long long per = (long long)H * dv * dk;                                                             \
+            lp_launch(gla_combine_kernel, dim3((unsigned)((per + 255) / 256), B), 256, 0, stream, state, slots,       \
+                      q_start, chunk_state, (const float*)chunk_decay, H, dk, dv, chunks, chunk);                     \
+            lp_launch(gla_scan_kernel<KP_, VT_, N>, grid, VT_ * KP_, smem, stream, proj, ld, q_off, k_off, v_off,     \
+                      decay, state, slots, q_start, out, H, dk, dv, q_scale, SCAN_OUTPUT, chunks, chunk, chunk_state, \
+                      chunk_decay);                                                                                   \
+        }                                                                                                             \
     } while (0)
     // few key channels: 4 threads per column, 64 columns per CTA; from 32 channels on: 16 threads per column, 16 columns
     if (dk <= 8) LP_LAUNCH_SCAN(4, 64, 2);

@@ -65,11 +65,12 @@ _SIGNATURES = {
         "lp_latent_absorb": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _P],
         "lp_latent_attend_rows": [],
         "lp_latent_attend": [_P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+        "lp_latent_merge": [_P, _I, _P, _I, _I, _P],
         "lp_latent_expand": [_P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P],
     },
     "linear_attention": {
         "lp_gla_decay": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _F, _P],
-        "lp_gla_scan": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _P],
+        "lp_gla_scan": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _P],
         "lp_gla_finish": [_P, _P, _F, _P, _I, _P, _I, _I, _I, _I, _P],
     },
     "host_loop": {
@@ -1134,6 +1135,19 @@ def latent_attend(q_abs: torch.Tensor, pages: torch.Tensor, page_table: torch.Te
     return partials
 
 
+def latent_merge(partials: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """The shares of every (token, head) row of ``partials`` [T, H, shares, rank + 2] merged into one share
+    ``out`` [T, H, 1, rank + 2] whose sum of weights is one."""
+    _want(partials, "latent_merge partials", torch.float32, 4)
+    _want(out, "latent_merge out", torch.float32, 4)
+    T, H, shares, width = partials.shape
+    if out.shape != (T, H, 1, width):
+        raise KernelError(f"latent_merge: partials {tuple(partials.shape)}, out {tuple(out.shape)}")
+    lib = library("latent_attention")
+    _check(lib, lib.lp_latent_merge(partials.data_ptr(), shares, out.data_ptr(), T * H, width - 2, _stream()))
+    return out
+
+
 def latent_expand(partials: torch.Tensor, v_up: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, *,
                   value_dim: int) -> torch.Tensor:
     """out[t, h * dv + v] = sigmoid(gate[t, h]) * (v_up[h] latent[t, h])[v], the latent being the merge of the
@@ -1177,13 +1191,20 @@ def gla_decay(low: torch.Tensor, up: torch.Tensor, bias: Optional[torch.Tensor],
     return out
 
 
+GLA_CHUNK = 128               # tokens per chunk of a long prompt's recurrence
+GLA_CHUNKED_FROM = 256        # from how many new tokens of a sequence on the chunks run side by side
+
+
 def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torch.Tensor, state: torch.Tensor,
              slots: torch.Tensor, q_start: torch.Tensor, out: torch.Tensor, *, num_heads: int, key_dim: int,
-             value_dim: int, q_scale: float) -> torch.Tensor:
+             value_dim: int, q_scale: float, max_new: int = 0, scratch=None) -> torch.Tensor:
     """The recurrence S <- diag(decay_t) S + k_t v_t^T, out_t = S^T (q_t * q_scale) over the step's tokens of every
     sequence, from and into ``state`` float32 [slots, H, dv, dk] (row ``slots[b]`` for sequence b; a value column's
     key channels lie together). ``proj``: float32
-    [T, F] with queries, keys and values at the given columns; ``decay``: float32 [T, H * dk]; ``out``: float32 [T, H * dv]."""
+    [T, F] with queries, keys and values at the given columns; ``decay``: float32 [T, H * dk]; ``out``: float32 [T, H * dv].
+    With ``max_new`` (the most new tokens of a sequence) of ``GLA_CHUNKED_FROM`` or more and ``scratch(name, shape,
+    dtype)`` for buffers, the sequences are cut into chunks of ``GLA_CHUNK`` tokens that run side by side: each
+    chunk's own contribution from a zero state, then the chunks' start states in order, then the outputs."""
     _want(proj, "gla_scan proj", torch.float32, 2)
     _want(decay, "gla_scan decay", torch.float32, 2)
     _want(state, "gla_scan state", torch.float32, 4)
@@ -1197,10 +1218,17 @@ def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torc
             or q_start.numel() != B + 1):
         raise KernelError(f"gla_scan: proj {tuple(proj.shape)}, decay {tuple(decay.shape)}, state {tuple(state.shape)}, "
                           f"out {tuple(out.shape)}, {B} sequences")
+    chunks, chunk_state, chunk_decay = 1, None, None
+    if scratch is not None and max_new >= GLA_CHUNKED_FROM and B * -(-max_new // GLA_CHUNK) <= 65535:
+        chunks = -(-max_new // GLA_CHUNK)
+        chunk_state = scratch("gla_chunk_states", (B, chunks, H, dv, dk), torch.float32)
+        chunk_decay = scratch("gla_chunk_decays", (B, chunks, H, dk), torch.float32)
     lib = library("linear_attention")
     _check(lib, lib.lp_gla_scan(proj.data_ptr(), proj.shape[1], int(q_off), int(k_off), int(v_off), decay.data_ptr(),
                                 state.data_ptr(), slots.data_ptr(), q_start.data_ptr(), out.data_ptr(), B, H, dk, dv,
-                                float(q_scale), _stream()))
+                                float(q_scale), chunks, GLA_CHUNK, _ptr(chunk_state), _ptr(chunk_decay), _stream()))
+    if chunks > 1:
+        count_launches(2)
     return out
 
 

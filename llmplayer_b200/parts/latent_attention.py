@@ -113,6 +113,10 @@ class LatentAttention(Part):
         o = ctx.buffer("attn_out", (T, H * dv), rt.act_dtype)
         gate = proj[:, gate_off:gate_off + H] if s.out_gate is not None else None
         with ops.section("attention.values"):
+            if shares > 2:
+                # many shares: one CTA per row merges them, so that the value map's CTAs need not each do it
+                merged = ctx.buffer("latent_merged", (T, H, 1, rank + 2), torch.float32)
+                partials = ops.latent_merge(partials, merged)
             ops.latent_expand(partials, self.v_up, gate, o, value_dim=dv)
         with ops.section("attention.out"):
             self.out.store(o, out, ctx)

@@ -96,7 +96,7 @@ class GatedLinearAttention(Part):
         raw = ctx.buffer("gla_raw", (T, H * dv), torch.float32)
         with ops.section("recurrence.scan"):
             ops.gla_scan(proj, q_off, k_off, v_off, decay, cache.rows, ctx.slots, ctx.q_start, raw, num_heads=H,
-                         key_dim=dk, value_dim=dv, q_scale=float(dk) ** -0.5)
+                         key_dim=dk, value_dim=dv, q_scale=float(dk) ** -0.5, max_new=ctx.max_new, scratch=ctx.buffer)
         o = ctx.buffer("attn_out", (T, H * dv), rt.act_dtype)
         with ops.section("recurrence.norm"):
             ops.gla_finish(raw, self.out_gain, s.norm_eps, proj[:, g_off:g_off + H * dv], o, num_heads=H, value_dim=dv)

@@ -25,7 +25,7 @@ def vocab(name):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name,length", [("small", 1), ("small", 2), ("small", 97), ("wide", 33), ("wide", 200)])
+@pytest.mark.parametrize("name,length", [("small", 1), ("small", 2), ("small", 97), ("small", 300), ("wide", 33), ("wide", 200), ("wide", 321)])
 def test_whole_sequence(tmp_path, name, length, dtype):
     from llmplayer_b200 import Engine
     model_dir = make_model(tmp_path, name, dtype)

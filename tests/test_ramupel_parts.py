@@ -196,7 +196,7 @@ def test_latent_attention_finds_one_key_among_hundreds(target):
 
 
 # --------------------------------------------------------------------------- gated linear attention
-def run_gla(H, dk, dv, q, k, v, z_low, up, bias, gate, gain, tau, state, slots, counts):
+def run_gla(H, dk, dv, q, k, v, z_low, up, bias, gate, gain, tau, state, slots, counts, chunked=False):
     from llmplayer_b200.kernels import ops
     T = q.shape[0]
     R = z_low.shape[1]
@@ -208,8 +208,14 @@ def run_gla(H, dk, dv, q, k, v, z_low, up, bias, gate, gain, tau, state, slots, 
     for n in counts:
         q_start.append(q_start[-1] + n)
     raw = torch.empty(T, H * dv, device="cuda")
+    kept = {}
+
+    def scratch(name, shape, dtype):
+        kept[name] = torch.full(shape, float("nan"), dtype=dtype, device="cuda")      # nothing may be read before it is written
+        return kept[name]
     ops.gla_scan(proj, 0, H * dk, 2 * H * dk, decay, state, i32(slots), i32(q_start), raw, num_heads=H, key_dim=dk,
-                 value_dim=dv, q_scale=dk ** -0.5)
+                 value_dim=dv, q_scale=dk ** -0.5, max_new=max(counts) if chunked else 0, scratch=scratch if chunked else None)
+    assert bool(kept) == (chunked and max(counts) >= ops.GLA_CHUNKED_FROM)
     out = torch.empty(T, H * dv, device="cuda")
     ops.gla_finish(raw, gain.float().cuda(), 1e-5, proj[:, 2 * H * dk + H * dv:a_off], out, num_heads=H, value_dim=dv)
     return out, decay
@@ -251,6 +257,35 @@ def test_gated_linear_attention_over_steps_and_slots(H, dk, dv, R):
     check_error("gated linear attention, float32", "final state", rel(state[4].transpose(1, 2), refs[0][1]), 3e-5)
     check_error("gated linear attention, float32", "final state", rel(state[1].transpose(1, 2), refs[1][1]), 3e-5)
     assert float((state[0] - 7.0).abs().max()) == 0.0 and float((state[5] - 7.0).abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("H,dk,dv", [(2, 20, 36), (1, 64, 80)])
+def test_gated_linear_attention_in_chunks_side_by_side(H, dk, dv):
+    """Long prompts (700, 300 and 5 tokens, so sequences with six, three and one chunk in one launch) whose chunks run
+    side by side, continuing states that are not zero; outputs and final states against the plain recurrence."""
+    g = torch.Generator().manual_seed(dk)
+    R, tau, counts = 4, 6.0, [700, 300, 5]
+
+    def draw(*shape, scale=1.0):
+        return scale * torch.randn(*shape, generator=g, dtype=torch.float64)
+    up, bias, gain = draw(H * dk, R, scale=0.6), 2.5 + 2 * draw(H * dk), 1 + 0.2 * draw(dv)
+    start = [draw(H, dk, dv) for _ in counts]
+    seqs = [{"q": draw(n, H, dk), "k": draw(n, H, dk), "v": draw(n, H, dv), "low": draw(n, R), "gate": draw(n, H * dv)}
+            for n in counts]
+    refs = []
+    for s0, s in zip(start, seqs):
+        a = (torch.sigmoid(s["low"] @ up.T + bias) ** (1 / tau)).reshape(-1, H, dk)
+        refs.append(P.gla_core(s["q"] * dk ** -0.5, s["k"], s["v"], a, s["gate"], gain, 1e-5, state=s0))
+    state = torch.zeros(4, H, dv, dk, device="cuda")
+    slots = [2, 0, 3]
+    for slot, s0 in zip(slots, start):
+        state[slot] = s0.transpose(1, 2).float().cuda()
+    pick = lambda key: torch.cat([s[key] for s in seqs])
+    out, _ = run_gla(H, dk, dv, pick("q"), pick("k"), pick("v"), pick("low"), up, bias, pick("gate"), gain, tau, state, slots,
+                     counts, chunked=True)
+    check_error("gated linear attention, chunks side by side", f"H{H} dk{dk} outputs", rel(out, torch.cat([r[0] for r in refs])), 3e-5)
+    for slot, r in zip(slots, refs):
+        check_error("gated linear attention, chunks side by side", "final state", rel(state[slot].transpose(1, 2), r[1]), 3e-5)
 
 
 def test_gated_linear_attention_remembers_an_early_token():
