@@ -38,8 +38,9 @@ gla_decay_kernel(const float* __restrict__ low, int ldl, const TW* __restrict__ 
 }
 
 // ---------------------------------------------------------------- scan
-// One CTA per (block of VT value columns, head, sequence); KP threads share a value column j, thread (j, part)
-// keeping the state entries of key channels part, part + KP, part + 2 KP, ... of that column in registers.
+// One CTA per (block of VT value columns, head, sequence); KP threads share JT neighbouring value columns, thread
+// (column group, part) keeping the state entries of key channels part, part + KP, part + 2 KP, ... of those columns
+// in registers.
 // Tokens are brought to shared memory TB at a time; per token every thread decays and updates its entries,
 // forms its share of o_t[j], and the KP shares meet in log2(KP) shuffles. The state is stored per head as
 // [dv, dk] (a column's channels lie together), so that the threads of a column read and write whole sectors.
@@ -55,8 +56,8 @@ constexpr int TB = 16;            // tokens per round of loads
 // mode WHOLE is the recurrence in one pass, from and into the sequence's state row (decode steps, short prompts).
 constexpr int SCAN_WHOLE = 0, SCAN_LOCAL = 1, SCAN_OUTPUT = 2;
 
-template <int KP, int VT, int KPT>
-__global__ void __launch_bounds__(VT * KP)
+template <int KP, int VT, int KPT, int JT>
+__global__ void __launch_bounds__(VT / JT * KP)
 gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off, const float* __restrict__ decay,
                 float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ q_start,
                 float* __restrict__ out, int H, int dk, int dv, float q_scale, int mode, int chunks, int chunk,
@@ -69,22 +70,25 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
     lp_grid_release();
     lp_grid_wait();
     const int h = blockIdx.y, b = blockIdx.z / chunks, piece = blockIdx.z - b * chunks;
-    const int tid = threadIdx.x, part = tid % KP, jl = tid / KP;
-    const int j = blockIdx.x * VT + jl;
-    const bool live = j < dv;
+    // thread (column group jg, part): JT neighbouring value columns, so that a token's decays, keys and queries are
+    // read from shared memory once for JT columns
+    const int tid = threadIdx.x, part = tid % KP, jg = tid / KP;
+    const int j0 = blockIdx.x * VT + jg * JT;
     int t0 = q_start[b], t1 = q_start[b + 1];
     if (mode != SCAN_WHOLE) {
         t0 += piece * chunk;
         t1 = min(t1, t0 + chunk);
         if (t0 >= t1) return;                             // this sequence has fewer chunks
     }
-    float* S = mode == SCAN_WHOLE ? state + (((long long)slots[b] * H + h) * dv + (live ? j : 0)) * dk
-                                  : chunk_state + (((long long)blockIdx.z * H + h) * dv + (live ? j : 0)) * dk;
-    float s[KPT], prod[KPT];
+    float* S = mode == SCAN_WHOLE ? state + ((long long)slots[b] * H + h) * dv * dk
+                                  : chunk_state + ((long long)blockIdx.z * H + h) * dv * dk;
+    float s[KPT][JT], prod[KPT];
 #pragma unroll
     for (int i = 0; i < KPT; ++i) {
         const int c = part + KP * i;
-        s[i] = (mode != SCAN_LOCAL && live && c < dk) ? S[c] : 0.f;
+#pragma unroll
+        for (int jj = 0; jj < JT; ++jj)
+            s[i][jj] = (mode != SCAN_LOCAL && j0 + jj < dv && c < dk) ? S[(long long)(j0 + jj) * dk + c] : 0.f;
         prod[i] = 1.f;
     }
     for (int tb = t0; tb < t1; tb += TB) {
@@ -103,49 +107,49 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
             vs[e] = col < dv ? proj[(long long)(tb + i) * ld + v_off + h * dv + col] : 0.f;
         }
         __syncthreads();
-        // the state runs through the tokens in order; each token's share of o_t[j] is kept, and the shares of all
-        // tokens of the round meet afterwards (shuffles that do not wait on one another)
-        float share[TB];
+        for (int i = 0; i < nt; ++i) {
+            float v[JT], acc[JT];
 #pragma unroll
-        for (int i = 0; i < TB; ++i) {
-            share[i] = 0.f;
-            if (i < nt) {
-                const float v = vs[i * VT + jl];
-                const float* qi = qs + i * dk;
-                const float* ki = ks + i * dk;
-                const float* ai = as + i * dk;
-                float acc0 = 0.f, acc1 = 0.f;
+            for (int jj = 0; jj < JT; ++jj) {
+                v[jj] = vs[i * VT + jg * JT + jj];
+                acc[jj] = 0.f;
+            }
+            const float* qi = qs + i * dk;
+            const float* ki = ks + i * dk;
+            const float* ai = as + i * dk;
 #pragma unroll
-                for (int u = 0; u < KPT; ++u) {
-                    const int c = part + KP * u;
-                    if (c < dk) {
-                        s[u] = fmaf(ai[c], s[u], ki[c] * v);
-                        if (mode == SCAN_LOCAL) prod[u] *= ai[c];
-                        if (u & 1) acc1 = fmaf(s[u], qi[c], acc1);
-                        else acc0 = fmaf(s[u], qi[c], acc0);
+            for (int u = 0; u < KPT; ++u) {
+                const int c = part + KP * u;
+                if (c < dk) {
+                    const float a = ai[c], k = ki[c], q = qi[c];
+                    if (mode == SCAN_LOCAL) prod[u] *= a;
+#pragma unroll
+                    for (int jj = 0; jj < JT; ++jj) {
+                        s[u][jj] = fmaf(a, s[u][jj], k * v[jj]);
+                        acc[jj] = fmaf(s[u][jj], q, acc[jj]);
                     }
                 }
-                share[i] = acc0 + acc1;
             }
-        }
+            if (mode != SCAN_LOCAL) {
 #pragma unroll
-        for (int o = 1; o < KP; o <<= 1) {
+                for (int o = 1; o < KP; o <<= 1) {
 #pragma unroll
-            for (int i = 0; i < TB; ++i) share[i] += __shfl_xor_sync(0xffffffffu, share[i], o);
-        }
+                    for (int jj = 0; jj < JT; ++jj) acc[jj] += __shfl_xor_sync(0xffffffffu, acc[jj], o);
+                }
 #pragma unroll
-        if (mode != SCAN_LOCAL) {
-#pragma unroll
-            for (int i = 0; i < TB; ++i)
-                if (i < nt && part == (i % KP) && live) out[((long long)(tb + i) * H + h) * dv + j] = share[i];
+                for (int jj = 0; jj < JT; ++jj)
+                    if (part == jj % KP && j0 + jj < dv) out[((long long)(tb + i) * H + h) * dv + j0 + jj] = acc[jj];
+            }
         }
     }
     if (mode == SCAN_OUTPUT) return;
 #pragma unroll
     for (int i = 0; i < KPT; ++i) {
         const int c = part + KP * i;
-        if (live && c < dk) S[c] = s[i];
-        if (mode == SCAN_LOCAL && blockIdx.x == 0 && jl == 0 && c < dk)
+#pragma unroll
+        for (int jj = 0; jj < JT; ++jj)
+            if (j0 + jj < dv && c < dk) S[(long long)(j0 + jj) * dk + c] = s[i][jj];
+        if (mode == SCAN_LOCAL && blockIdx.x == 0 && jg == 0 && c < dk)
             chunk_decay[((long long)blockIdx.z * H + h) * dk + c] = prod[i];
     }
 }
@@ -236,38 +240,39 @@ extern "C" int lp_gla_scan(const float* proj, int ld, int q_off, int k_off, int 
     if (dk > 512) LP_REFUSE("gla_scan: %d key channels per head (supported: up to 512)", dk);
     if (q_off < 0 || k_off < 0 || v_off < 0 || q_off + H * dk > ld || k_off + H * dk > ld || v_off + H * dv > ld)
         LP_REFUSE("gla_scan: slices at %d, %d, %d do not fit rows of %d", q_off, k_off, v_off, ld);
-#define LP_LAUNCH_SCAN(KP_, VT_, N)                                                                                   \
+#define LP_LAUNCH_SCAN(KP_, VT_, N, JT_)                                                                                 \
     do {                                                                                                              \
         dim3 grid((dv + VT_ - 1) / VT_, H, B * chunks);                                                               \
         const size_t smem = ((size_t)3 * TB * dk + (size_t)TB * VT_) * sizeof(float);                                 \
         if (smem > 48 * 1024) {                                                                                       \
-            cudaError_t e = cudaFuncSetAttribute(gla_scan_kernel<KP_, VT_, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            cudaError_t e = cudaFuncSetAttribute(gla_scan_kernel<KP_, VT_, N, JT_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) LP_REFUSE("gla_scan: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e)); \
         }                                                                                                             \
         if (chunks == 1) {                                                                                            \
-            lp_launch(gla_scan_kernel<KP_, VT_, N>, grid, VT_ * KP_, smem, stream, proj, ld, q_off, k_off, v_off,     \
+            lp_launch(gla_scan_kernel<KP_, VT_, N, JT_>, grid, VT_ / JT_ * KP_, smem, stream, proj, ld, q_off, k_off, v_off,     \
                       decay, state, slots, q_start, out, H, dk, dv, q_scale, SCAN_WHOLE, 1, 0, (float*)nullptr,       \
                       (float*)nullptr);                                                                               \
         } else {                                                                                                      \
-            lp_launch(gla_scan_kernel<KP_, VT_, N>, grid, VT_ * KP_, smem, stream, proj, ld, q_off, k_off, v_off,     \
+            lp_launch(gla_scan_kernel<KP_, VT_, N, JT_>, grid, VT_ / JT_ * KP_, smem, stream, proj, ld, q_off, k_off, v_off,     \
                       decay, state, slots, q_start, out, H, dk, dv, q_scale, SCAN_LOCAL, chunks, chunk, chunk_state,  \
                       chunk_decay);                                                                                   \
             const long long per = (long long)H * dv * dk;                                                             \
             lp_launch(gla_combine_kernel, dim3((unsigned)((per + 255) / 256), B), 256, 0, stream, state, slots,       \
                       q_start, chunk_state, (const float*)chunk_decay, H, dk, dv, chunks, chunk);                     \
-            lp_launch(gla_scan_kernel<KP_, VT_, N>, grid, VT_ * KP_, smem, stream, proj, ld, q_off, k_off, v_off,     \
+            lp_launch(gla_scan_kernel<KP_, VT_, N, JT_>, grid, VT_ / JT_ * KP_, smem, stream, proj, ld, q_off, k_off, v_off,     \
                       decay, state, slots, q_start, out, H, dk, dv, q_scale, SCAN_OUTPUT, chunks, chunk, chunk_state, \
                       chunk_decay);                                                                                   \
         }                                                                                                             \
     } while (0)
     // few key channels: 4 threads per column, 64 columns per CTA; from 32 channels on: 16 threads per column, 16 columns
-    if (dk <= 8) LP_LAUNCH_SCAN(4, 64, 2);
-    else if (dk <= 16) LP_LAUNCH_SCAN(4, 64, 4);
-    else if (dk < 32) LP_LAUNCH_SCAN(4, 64, 8);
-    else if (dk <= 64) LP_LAUNCH_SCAN(16, 16, 4);
-    else if (dk <= 128) LP_LAUNCH_SCAN(16, 16, 8);
-    else if (dk <= 256) LP_LAUNCH_SCAN(16, 16, 16);
-    else LP_LAUNCH_SCAN(16, 16, 32);
+    // (threads per column, columns per CTA, channels per thread, columns per thread): 256 threads in every form
+    if (dk <= 8) LP_LAUNCH_SCAN(4, 64, 2, 1);
+    else if (dk <= 16) LP_LAUNCH_SCAN(4, 64, 4, 1);
+    else if (dk < 32) LP_LAUNCH_SCAN(4, 64, 8, 1);
+    else if (dk <= 64) LP_LAUNCH_SCAN(16, 64, 4, 4);
+    else if (dk <= 128) LP_LAUNCH_SCAN(16, 64, 8, 4);
+    else if (dk <= 256) LP_LAUNCH_SCAN(16, 32, 16, 2);
+    else LP_LAUNCH_SCAN(16, 16, 32, 1);
 #undef LP_LAUNCH_SCAN
     return lp_check_launch("gla_scan");
 }
