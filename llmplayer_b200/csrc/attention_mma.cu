@@ -453,6 +453,7 @@ extern "C" int lp_attention_prefill(const void* q, void* out, const void* pages,
     else if (hd == 64) LP_PREFILL_EXACT(64, 64);
     else if (hd == 128 && tall) LP_PREFILL_EXACT(128, 128);
     else if (hd == 128) LP_PREFILL_EXACT(128, 64);
+    else if (hd == 192) LP_PREFILL_EXACT(192, 64);      // rows of 24 sixteen-byte chunks keep the same swizzle
     else if (hd <= 64) LP_PREFILL(64); else if (hd <= 96) LP_PREFILL(96); else if (hd <= 128) LP_PREFILL(128);
     else if (hd <= 192) LP_PREFILL(192); else LP_PREFILL(256);       // 96 and 192: heads of 64 + 32 and 128 + 64
 #undef LP_PREFILL_EXACT

@@ -134,7 +134,8 @@ def run_case(kind, lengths, new, H, G, hd, window, dtype, seed=0, crafted=False,
     return err
 
 
-GEOMETRIES = [(4, 2, 16), (3, 1, 32), (6, 3, 48), (32, 8, 64), (8, 2, 128), (2, 2, 256), (20, 1, 64)]
+GEOMETRIES = [(4, 2, 16), (3, 1, 32), (6, 3, 48), (32, 8, 64), (8, 2, 128), (2, 2, 256), (20, 1, 64), (4, 4, 96),
+              (6, 2, 192)]
 
 
 @pytest.mark.parametrize("H,G,hd", GEOMETRIES)
