@@ -270,9 +270,10 @@ def hybrid_rooflines(size, layers, row, peaks, batch, context, n):
 
     def frac(work, ms, count, peak):
         return None if not ms or not count else work / (ms / count / 1e3) / peak
-    # prompt attention: causal scores and weighted sums
+    # prompt attention: causal scores and weighted sums (the latent layers in the form they run in for prompts:
+    # per head, keys of dim + rot_dim and values of vdim)
     out["prefill latent attention (of tensor peak)"] = frac(
-        heads * n * (n + 1) * ((rank + dr) + rank), r["prefill_sections_ms"].get("attention.scores"), n_lat, flops)
+        heads * n * (n + 1) * ((dn + dr) + dv), r["prefill_sections_ms"].get("attention.scores"), n_lat, flops)
     out["prefill llama attention (of tensor peak)"] = frac(
         heads * n * (n + 1) * 2 * hd, l["prefill_sections_ms"].get("attention.scores"), layers, flops)
     out["prefill gla recurrence (of tensor peak)"] = frac(

@@ -32,7 +32,7 @@ latent_prepare_kernel(const float* __restrict__ proj, int ld, int q_off, int kv_
                       const int* __restrict__ seq_ids, const int* __restrict__ page_table, int pt_stride,
                       float* __restrict__ q_out, TKV* __restrict__ pages, int H, int dn, int dr, int rank,
                       int page_size, __nv_bfloat16* __restrict__ latent_out, __nv_bfloat16* __restrict__ shared_out,
-                      __nv_bfloat16* __restrict__ q_half) {
+                      __nv_bfloat16* __restrict__ q_half, int q_half_hd) {
     __shared__ float cs[128], sn[128];
     __shared__ float scratch[32];
     lp_grid_release();
@@ -76,7 +76,12 @@ latent_prepare_kernel(const float* __restrict__ proj, int ld, int q_off, int kv_
             else if (i < rot) v = __fadd_rn(__fmul_rn(q[e], cs[i - half]), __fmul_rn(q[e - half], sn[i - half]));
         }
         qo[e] = v;
-        if (q_half) q_half[(long long)t * H * hd + e] = __float2bfloat16_rn(v);
+        if (q_half) q_half[((long long)t * H + e / hd) * q_half_hd + e % hd] = __float2bfloat16_rn(v);
+    }
+    if (q_half && q_half_hd > hd) {                       // heads padded with zeros to a size the attention kernels take
+        const int pad = q_half_hd - hd;
+        for (int e = tid; e < H * pad; e += blockDim.x)
+            q_half[((long long)t * H + e / pad) * q_half_hd + hd + e % pad] = __float2bfloat16_rn(0.f);
     }
 }
 
@@ -84,17 +89,17 @@ latent_prepare_kernel(const float* __restrict__ proj, int ld, int q_off, int kv_
 // For steps whose sequences all start at their first token, the heads' keys and values are formed outright
 // (one product with the stacked key and value maps) and laid out as pages of keys and values, so that the
 // tensor-core attention of ordinary heads serves: key of head h = [its unrotated part | the shared rotated
-// part], value of head h padded with zeros to the key's size. kv: bfloat16 [T, H * dn + H * dv].
+// part], both padded with zeros to heads of hd >= dn + dr (a size the attention kernels are built for), value of
+// head h likewise. kv: bfloat16 [T, H * dn + H * dv].
 __global__ void __launch_bounds__(256)
 latent_heads_to_pages_kernel(const __nv_bfloat16* __restrict__ kv, const __nv_bfloat16* __restrict__ shared_part,
                              const int* __restrict__ positions, const int* __restrict__ seq_ids,
                              const int* __restrict__ table, int pt_stride, const int* __restrict__ kv_len,
-                             __nv_bfloat16* __restrict__ pages, int H, int dn, int dr, int dv, int page_size) {
+                             __nv_bfloat16* __restrict__ pages, int H, int dn, int dr, int dv, int page_size, int hd) {
     lp_grid_release();
     lp_grid_wait();
     const int t = blockIdx.x;
     const int pos = positions[t];
-    const int hd = dn + dr;
     const int seq = seq_ids[t];
     const long long page = table[(long long)seq * pt_stride + pos / page_size];
     __nv_bfloat16* kdst = pages + page * 2 * H * page_size * hd + (long long)(pos % page_size) * hd;
@@ -104,7 +109,7 @@ latent_heads_to_pages_kernel(const __nv_bfloat16* __restrict__ kv, const __nv_bf
     for (int e = threadIdx.x; e < H * hd; e += blockDim.x) {
         const int h = e / hd, i = e - h * hd;
         const long long at = (long long)h * page_size * hd + i;
-        kdst[at] = i < dn ? row[h * dn + i] : shared_part[(long long)t * dr + i - dn];
+        kdst[at] = i < dn ? row[h * dn + i] : (i < dn + dr ? shared_part[(long long)t * dr + i - dn] : zero);
         vdst[at] = i < dv ? row[H * dn + h * dv + i] : zero;
     }
     // the sequence's last token also clears the rest of its last page: the attention kernel multiplies those rows
@@ -161,7 +166,7 @@ latent_absorb_kernel(const float* __restrict__ q, const TW* __restrict__ uk, flo
         float acc[TOK_TILE];
 #pragma unroll
         for (int i = 0; i < TOK_TILE; ++i) acc[i] = 0.f;
-#pragma unroll 8
+#pragma unroll 16
         for (int d = 0; d < dn; ++d) {
             const float w = lp_to_float(u[(long long)d * rank + r]);
 #pragma unroll
@@ -233,14 +238,22 @@ latent_attend_kernel(const float* __restrict__ qa, const TKV* __restrict__ pages
     for (int blk = blk_lo; blk < blk_hi; ++blk) {
         const int k0 = blk * KEYS;
         __syncthreads();                                  // the previous block has been used (and Qs is written)
-        for (int j = warp; j < KEYS; j += WARPS) {
-            const int kp = k0 + j;
-            float* dst = Ks + j * KS;
-            if (kp <= last_pos) {
-                const TKV* src = pages + ((long long)pt[kp / page_size] * page_size + kp % page_size) * Dk;
-                for (int e = lane; e < Dk; e += 32) dst[e] = lp_to_float(src[e]);
-            } else {
-                for (int e = lane; e < Dk; e += 32) dst[e] = 0.f;
+        {
+            // a warp brings keys warp, warp + 8, warp + 16, warp + 24 together, so that four loads are in flight per lane
+            constexpr int PER = KEYS / WARPS;
+            const TKV* src[PER];
+#pragma unroll
+            for (int u = 0; u < PER; ++u) {
+                const int kp = k0 + warp + u * WARPS;
+                src[u] = kp <= last_pos ? pages + ((long long)pt[kp / page_size] * page_size + kp % page_size) * Dk : nullptr;
+            }
+#pragma unroll 2
+            for (int e = lane; e < Dk; e += 32) {
+                float v[PER];
+#pragma unroll
+                for (int u = 0; u < PER; ++u) v[u] = src[u] ? lp_to_float(src[u][e]) : 0.f;
+#pragma unroll
+                for (int u = 0; u < PER; ++u) Ks[(warp + u * WARPS) * KS + e] = v[u];
             }
         }
         __syncthreads();
@@ -414,6 +427,7 @@ latent_expand_kernel(const float* __restrict__ part, int shares, const TW* __res
         float acc[TOK_TILE];
 #pragma unroll
         for (int i = 0; i < TOK_TILE; ++i) acc[i] = 0.f;
+#pragma unroll 8
         for (int r = lane; r < rank; r += 32) {
             const float wv = lp_to_float(w[r]);
 #pragma unroll
@@ -444,23 +458,25 @@ int grant_shared(K kernel, size_t bytes, const char* what) {
 
 // proj: float32 [T, ld] with the queries at q_off ([H, dn + dr]) and the latent and shared key part at kv_off
 // ([rank + dr]); pages: [num_pages, page_size, rank + dr]; q_out: float32 [T, H, dn + dr]. Optional bfloat16
-// copies that lie together: latent_out [T, rank], shared_out [T, dr], q_half [T, H, dn + dr].
+// copies that lie together: latent_out [T, rank], shared_out [T, dr], q_half [T, H, q_half_hd] (heads padded with
+// zeros from dn + dr to q_half_hd).
 extern "C" int lp_latent_prepare(const float* proj, int ld, int q_off, int kv_off, const float* gain, float eps,
                                  const float* inv_freq, int rot, const int* positions, const int* seq_ids,
                                  const int* page_table, int pt_stride, float* q_out, void* pages, int kv_dtype, int T,
                                  int H, int dn, int dr, int rank, int page_size, void* latent_out, void* shared_out,
-                                 void* q_half, cudaStream_t stream) {
+                                 void* q_half, int q_half_hd, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || dn < 0 || dr < 0 || rank <= 0 || dn + dr <= 0) LP_REFUSE("latent_prepare: %d heads of %d + %d over rank %d", H, dn, dr, rank);
     if (rot < 0 || (rot & 1) || rot > dr || rot > 256) LP_REFUSE("latent_prepare: rotary width %d of %d (even, at most 256)", rot, dr);
     if (rot > 0 && !inv_freq) LP_REFUSE("latent_prepare: rotation without frequencies");
     if (page_size <= 0) LP_REFUSE("latent_prepare: page size %d", page_size);
+    if (q_half && q_half_hd < dn + dr) LP_REFUSE("latent_prepare: padded heads of %d for heads of %d", q_half_hd, dn + dr);
     if (q_off < 0 || kv_off < 0 || q_off + H * (dn + dr) > ld || kv_off + rank + dr > ld)
         LP_REFUSE("latent_prepare: slices at %d and %d do not fit rows of %d", q_off, kv_off, ld);
 #define LP_LAUNCH_PREP(TKV)                                                                                       \
     lp_launch(latent_prepare_kernel<TKV>, T, 256, 0, stream, proj, ld, q_off, kv_off, gain, eps, inv_freq, rot,    \
               positions, seq_ids, page_table, pt_stride, q_out, (TKV*)pages, H, dn, dr, rank, page_size,                   \
-              (__nv_bfloat16*)latent_out, (__nv_bfloat16*)shared_out, (__nv_bfloat16*)q_half)
+              (__nv_bfloat16*)latent_out, (__nv_bfloat16*)shared_out, (__nv_bfloat16*)q_half, q_half_hd)
     if (kv_dtype == LP_F32) LP_LAUNCH_PREP(float);
     else if (kv_dtype == LP_BF16) LP_LAUNCH_PREP(__nv_bfloat16);
     else LP_REFUSE("latent_prepare: cache dtype code %d", kv_dtype);
@@ -563,16 +579,17 @@ extern "C" int lp_latent_expand(const float* part, int shares, const void* uv, i
 }
 
 // kv: bfloat16 [T, H * dn + H * dv] (every head's unrotated keys, then every head's values); shared_part: bfloat16
-// [T, dr]; pages: bfloat16 [num_pages, 2, H, page_size, dn + dr]; table: [B, pt_stride]; kv_len [B]: the sequences'
+// [T, dr]; pages: bfloat16 [num_pages, 2, H, page_size, hd]; table: [B, pt_stride]; kv_len [B]: the sequences'
 // lengths, all of whose positions are in this step.
 extern "C" int lp_latent_heads_to_pages(const void* kv, const void* shared_part, const int* positions, const int* seq_ids,
                                         const int* table, int pt_stride, const int* kv_len, void* pages, int T, int H,
-                                        int dn, int dr, int dv, int page_size, cudaStream_t stream) {
+                                        int dn, int dr, int dv, int page_size, int hd, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (H <= 0 || dn < 0 || dr < 0 || dv <= 0 || dv > dn + dr) LP_REFUSE("latent_heads_to_pages: %d heads of %d + %d, values of %d", H, dn, dr, dv);
+    if (H <= 0 || dn < 0 || dr < 0 || dv <= 0 || hd < dn + dr || dv > hd)
+        LP_REFUSE("latent_heads_to_pages: %d heads of %d + %d in %d, values of %d", H, dn, dr, hd, dv);
     if (page_size <= 0) LP_REFUSE("latent_heads_to_pages: page size %d", page_size);
     lp_launch(latent_heads_to_pages_kernel, T, 256, 0, stream, (const __nv_bfloat16*)kv, (const __nv_bfloat16*)shared_part,
-              positions, seq_ids, table, pt_stride, kv_len, (__nv_bfloat16*)pages, H, dn, dr, dv, page_size);
+              positions, seq_ids, table, pt_stride, kv_len, (__nv_bfloat16*)pages, H, dn, dr, dv, page_size, hd);
     return lp_check_launch("latent_heads_to_pages");
 }
 

@@ -59,8 +59,8 @@ _SIGNATURES = {
     },
     "latent_attention": {
         "lp_latent_prepare": [_P, _I, _I, _I, _P, _F, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P,
-                              _P],
-        "lp_latent_heads_to_pages": [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+                              _I, _P],
+        "lp_latent_heads_to_pages": [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
         "lp_latent_gate_heads": [_P, _P, _I, _P, _I, _I, _I, _I, _P],
         "lp_latent_absorb": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _P],
         "lp_latent_attend_rows": [],
@@ -1010,7 +1010,7 @@ def latent_prepare(proj: torch.Tensor, q_off: int, kv_off: int, gain: torch.Tens
     part and write both into ``pages`` [num_pages, page_size, rank + rope] at the tokens' positions; rotate the
     queries' rope parts and write the queries to ``q_out`` float32 [T, H, nope + rope]. Optional bfloat16 copies
     that lie together, for a step that forms every head's keys and values outright: ``latent_out`` [T, rank],
-    ``shared_out`` [T, rope], ``q_half`` [T, H * (nope + rope)]."""
+    ``shared_out`` [T, rope], ``q_half`` [T, H * hd] with hd >= nope + rope (heads padded with zeros)."""
     _want(proj, "latent_prepare proj", torch.float32, 2)
     _want(gain, "latent_prepare gain", torch.float32, 1)
     _want(positions, "latent_prepare positions", torch.int32, 1)
@@ -1024,12 +1024,17 @@ def latent_prepare(proj: torch.Tensor, q_off: int, kv_off: int, gain: torch.Tens
             or positions.numel() != T or seq_ids.numel() != T):
         raise KernelError(f"latent_prepare: proj {tuple(proj.shape)}, q_out {tuple(q_out.shape)}, pages "
                           f"{tuple(pages.shape)} for {H} heads of {dn} + {dr} over rank {rank}")
-    for extra, shape, what in ((latent_out, (T, rank), "latent_out"), (shared_out, (T, dr), "shared_out"),
-                               (q_half, (T, H * (dn + dr)), "q_half")):
+    for extra, shape, what in ((latent_out, (T, rank), "latent_out"), (shared_out, (T, dr), "shared_out")):
         if extra is not None:
             _want(extra, f"latent_prepare {what}", torch.bfloat16, 2)
             if extra.shape != shape:
                 raise KernelError(f"latent_prepare: {what} {tuple(extra.shape)}, expected {shape}")
+    q_half_hd = 0
+    if q_half is not None:
+        _want(q_half, "latent_prepare q_half", torch.bfloat16, 2)
+        q_half_hd = q_half.shape[1] // H
+        if q_half.shape[0] != T or q_half.shape[1] != H * q_half_hd or q_half_hd < dn + dr:
+            raise KernelError(f"latent_prepare: q_half {tuple(q_half.shape)} for {H} heads of {dn + dr}")
     freq_ptr, rot, interleaved = rotation.checked("latent_prepare")
     if interleaved:
         raise KernelError("latent_prepare: pairs of neighbours are not supported, only (i, i + half)")
@@ -1038,15 +1043,15 @@ def latent_prepare(proj: torch.Tensor, q_off: int, kv_off: int, gain: torch.Tens
         proj.data_ptr(), proj.shape[1], int(q_off), int(kv_off), gain.data_ptr(), float(eps), freq_ptr, rot,
         positions.data_ptr(), seq_ids.data_ptr(), page_table.data_ptr(), page_table.shape[1], q_out.data_ptr(),
         pages.data_ptr(), _code(pages, "latent_prepare pages"), T, H, dn, dr, rank, pages.shape[1], _ptr(latent_out),
-        _ptr(shared_out), _ptr(q_half), _stream()))
+        _ptr(shared_out), _ptr(q_half), q_half_hd, _stream()))
 
 
 def latent_heads_to_pages(kv: torch.Tensor, shared_part: torch.Tensor, positions: torch.Tensor, seq_ids: torch.Tensor,
                           table: torch.Tensor, kv_len: torch.Tensor, pages: torch.Tensor, *, num_heads: int, nope_dim: int,
                           rope_dim: int, value_dim: int) -> None:
     """Lay the heads' keys and values of a step's tokens out as pages of ordinary keys and values
-    [num_pages, 2, H, page_size, nope + rope]: key of head h = [kv[t, h * nope + :] | shared_part[t]], value of
-    head h = kv[t, H * nope + h * dv + :] padded with zeros. All bfloat16; ``table`` [B, W] names the pages. The step
+    [num_pages, 2, H, page_size, hd] with hd >= nope + rope: key of head h = [kv[t, h * nope + :] | shared_part[t]],
+    value of head h = kv[t, H * nope + h * dv + :], both padded with zeros. All bfloat16; ``table`` [B, W] names the pages. The step
     holds every position of its sequences (``kv_len`` [B]); the rest of each sequence's last page is cleared."""
     H, dn, dr, dv = num_heads, nope_dim, rope_dim, value_dim
     _want(kv, "latent_heads_to_pages kv", torch.bfloat16, 2)
@@ -1056,13 +1061,13 @@ def latent_heads_to_pages(kv: torch.Tensor, shared_part: torch.Tensor, positions
     _want(kv_len, "latent_heads_to_pages kv_len", torch.int32, 1)
     T = kv.shape[0]
     if (kv.shape[1] != H * (dn + dv) or shared_part.shape != (T, dr) or pages.shape[1] != 2 or pages.shape[2] != H
-            or pages.shape[4] != dn + dr or positions.numel() != T or seq_ids.numel() != T):
+            or pages.shape[4] < dn + dr or positions.numel() != T or seq_ids.numel() != T):
         raise KernelError(f"latent_heads_to_pages: kv {tuple(kv.shape)}, shared part {tuple(shared_part.shape)}, pages "
                           f"{tuple(pages.shape)}")
     lib = library("latent_attention")
     _check(lib, lib.lp_latent_heads_to_pages(kv.data_ptr(), shared_part.data_ptr(), positions.data_ptr(), seq_ids.data_ptr(),
                                              table.data_ptr(), table.shape[1], kv_len.data_ptr(), pages.data_ptr(), T, H, dn, dr, dv,
-                                             pages.shape[3], _stream()))
+                                             pages.shape[3], pages.shape[4], _stream()))
 
 
 def latent_gate_heads(heads: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, *, num_heads: int,

@@ -130,16 +130,22 @@ class LatentAttention(Part):
         heads over them: the bfloat16 path, every sequence at its first token (nothing cached to attend over),
         enough tokens for it to pay, and head sizes that kernel takes."""
         s, rt = self.spec, self.runtime
-        hd = s.nope_dim + s.rope_dim
+        hd = self._padded_head()
         return (rt.fast and cache.pages.dtype == torch.bfloat16 and ctx.max_new >= self.HEADS_MIN_TOKENS
-                and all(p == 0 for p in ctx.first_positions) and hd % 16 == 0 and hd <= 256 and s.value_dim <= hd
+                and all(p == 0 for p in ctx.first_positions) and hd is not None and s.value_dim <= hd
                 and s.kv_rank % 8 == 0)
+
+    def _padded_head(self):
+        """The head size the prompt attention runs at: the next of 64, 128, 192, 256 (the sizes its kernels know at
+        compile time), queries, keys and values padded with zeros."""
+        need = self.spec.nope_dim + self.spec.rope_dim
+        return next((size for size in (64, 128, 192, 256) if need <= size), None)
 
     def _forward_heads(self, ctx, cache, proj, q_off, kv_off, gate_off, rotation, table, q, out):
         s = self.spec
         T = proj.shape[0]
         H, dn, dr, dv, rank = s.num_heads, s.nope_dim, s.rope_dim, s.value_dim, s.kv_rank
-        hd = dn + dr
+        hd = self._padded_head()
         page = cache.pages.shape[1]
         latent = ctx.buffer("latent_rows", (T, rank), torch.bfloat16)
         shared = ctx.buffer("latent_shared_key", (T, dr), torch.bfloat16)
