@@ -57,7 +57,7 @@ constexpr int TB = 16;            // tokens per round of loads
 constexpr int SCAN_WHOLE = 0, SCAN_LOCAL = 1, SCAN_OUTPUT = 2;
 
 template <int KP, int VT, int KPT, int JT>
-__global__ void __launch_bounds__(VT / JT * KP)
+__global__ void __launch_bounds__(VT / JT * KP, 3)
 gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off, const float* __restrict__ decay,
                 float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ q_start,
                 float* __restrict__ out, int H, int dk, int dv, float q_scale, int mode, int chunks, int chunk,

@@ -21,17 +21,23 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", required=True, choices=("bfloat16", "float32"))
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
+                    help="most tokens live requests hold at any time; the cache gets room beyond that for the partly "
+                         "filled last page of each live request")
     ap.add_argument("--device", default="cuda:0")
     ap.add_argument("--context-length", type=int, default=None,
                     help="longest request; default: the model's max_position_embeddings. A larger value is taken "
                          "as given (positions beyond what the model was made for)")
     args = ap.parse_args(argv)
 
+    from ..cache.pages import PAGE_SIZE
     from .engine import Engine
 
     os.makedirs(args.out, exist_ok=True)
-    engine = Engine.load(args.model, dtype=args.dtype, max_tokens=max(args.max_tokens, 64), device=args.device,
+    # every live request may leave up to a page less one position unused: room for 64 such requests, and for one
+    # more per 16 tokens (requests are rarely shorter on average), but never more than one page per token
+    tokens = max(args.max_tokens, 1)
+    spare_pages = min(tokens, 64 + tokens // 16)
+    engine = Engine.load(args.model, dtype=args.dtype, max_tokens=tokens + PAGE_SIZE * spare_pages, device=args.device,
                          context_length=args.context_length, beyond_model_context=args.context_length is not None)
     slots: Dict[str, int] = {}
     for line in sys.stdin:

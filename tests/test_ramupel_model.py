@@ -164,6 +164,31 @@ def test_greedy_generation_through_the_entry_point(tmp_path, name, dtype):
     assert compared == 60
 
 
+def test_sampled_generation_steps_the_state_once(tmp_path):
+    """The reference's default sampler (temperature, top-k, top-p, repetition penalty) with a seed: the captured
+    steps of the native host loop must draw the same tokens as plain stepping, which they only do if no step ever
+    ran twice over the recurrent state (a first step "for nothing" would decay and update it twice)."""
+    from llmplayer_b200 import Engine
+    from llmplayer_b200.sampling import SamplerConfig
+    model_dir = make_model(tmp_path, "wide", "bfloat16")
+    prompts = [random_tokens(n, vocab("wide"), seed=90 + n) for n in (12, 40, 3)]
+    fast = Engine.load(model_dir, dtype="bfloat16", max_tokens=512, max_slots=3)
+    slow = Engine.load(model_dir, dtype="bfloat16", max_tokens=512, max_slots=3, host_loop=False, graphs=False)
+    for round_ in range(2):                                # the second round re-uses slots, pages and captured graphs
+        a = fast.generate(prompts, SamplerConfig(seed=5 + round_), max_tokens=24, stop_token_ids=())
+        b = slow.generate(prompts, SamplerConfig(seed=5 + round_), max_tokens=24, stop_token_ids=())
+        assert [r.token_ids for r in a] == [r.token_ids for r in b]
+
+
+def test_command_line_generates(tmp_path):
+    model_dir = make_model(tmp_path, "small", "bfloat16")
+    proc = subprocess.run([sys.executable, "-m", "llmplayer_b200", "--model", model_dir, "--prompt", "5 17 3 99", "-n", "8",
+                           "--temperature", "0", "--context-length", "128"], capture_output=True, text=True, timeout=600,
+                          cwd=ROOT)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert "8 generated" in proc.stdout, proc.stdout
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_replay(tmp_path, dtype):
     """``bin/trace_run`` on a Ramupel folder: two requests together, then decoded together, one ending early."""
