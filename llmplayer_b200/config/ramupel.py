@@ -193,6 +193,10 @@ class RamupelConfig(ArchitectureConfig):
     def max_positions(self) -> int:
         return self.DEFAULT_CONTEXT
 
+    def ignorable_tensors(self) -> tuple:
+        # a layer without a feed-forward has no use for the feed-forward's gate, should a file carry one
+        return tuple(f"l{i}.rg2{suffix}" for i, layer in enumerate(self.layers) if layer.ff is None for suffix in ("", ".b"))
+
     def layout(self) -> ModelLayout:
         d = self.width
         total = len(self.layers) + 1

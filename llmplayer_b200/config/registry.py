@@ -45,6 +45,11 @@ class ArchitectureConfig:
     def max_positions(self) -> int:
         raise NotImplementedError
 
+    def ignorable_tensors(self) -> tuple:
+        """Names of tensors that a model file of this architecture may hold although the layout has no use for
+        them (the loader does not report them as unexpected)."""
+        return ()
+
 
 def register_architecture(name: str, config_cls: Type[ArchitectureConfig], *, replace: bool = False) -> None:
     if not name:

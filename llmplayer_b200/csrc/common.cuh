@@ -97,6 +97,17 @@ static inline int lp_sm_count() {
     return sms;
 }
 
+// A float32 buffer that a kernel clears on the side (all its blocks share the work), for a product later in the
+// step that sums partial results into it with atomics.
+__device__ __forceinline__ void clear_on_the_side(float* zero, long long zero_count) {
+    if (zero) {
+        const long long blocks = (long long)gridDim.x * gridDim.y * gridDim.z;
+        const long long block = ((long long)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+        const long long stride = blocks * blockDim.x;
+        for (long long i = block * blockDim.x + threadIdx.x; i < zero_count; i += stride) zero[i] = 0.f;
+    }
+}
+
 __device__ __forceinline__ float lp_to_float(float v) { return v; }
 __device__ __forceinline__ float lp_to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 

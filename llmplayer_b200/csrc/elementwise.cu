@@ -50,12 +50,6 @@ extern "C" int lp_embed(const void* table, int table_dtype, const int* tokens, f
 constexpr int NORM_THREADS = 256;
 constexpr int NORM_PER = 16;
 
-__device__ __forceinline__ void clear_on_the_side(float* zero, long long zero_count) {
-    if (zero) {
-        const long long stride = (long long)gridDim.x * blockDim.x;
-        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < zero_count; i += stride) zero[i] = 0.f;
-    }
-}
 
 template <typename TOut, typename TAdd>
 __global__ void __launch_bounds__(NORM_THREADS)
@@ -446,9 +440,11 @@ __device__ __forceinline__ float lp_softplus(float v) { return fmaxf(v, 0.f) + l
 
 template <typename TOut>
 __global__ void __launch_bounds__(256)
-xielu_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ pq, TOut* __restrict__ out, int T, int F) {
+xielu_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ pq, TOut* __restrict__ out, int T, int F,
+             float* __restrict__ zero, long long zero_count) {
     lp_grid_release();
     lp_grid_wait();
+    clear_on_the_side(zero, zero_count);
     const float ap = lp_softplus(pq[0]), an = 0.5f + lp_softplus(pq[1]);
     const long long n = (long long)T * F;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
@@ -463,9 +459,11 @@ xielu_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ pq,
 // The same, four values per thread (rows and row starts of a multiple of four values).
 template <typename TOut>
 __global__ void __launch_bounds__(256)
-xielu_vec4_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ pq, TOut* __restrict__ out, int T, int F) {
+xielu_vec4_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ pq, TOut* __restrict__ out, int T, int F,
+                  float* __restrict__ zero, long long zero_count) {
     lp_grid_release();
     lp_grid_wait();
+    clear_on_the_side(zero, zero_count);
     const float ap = lp_softplus(pq[0]), an = 0.5f + lp_softplus(pq[1]);
     const int quads = F >> 2;
     const long long n = (long long)T * quads;
@@ -489,26 +487,28 @@ xielu_vec4_kernel(const float* __restrict__ z, int ldz, const float* __restrict_
     }
 }
 
-extern "C" int lp_xielu(const float* z, int ldz, const float* pq, void* out, int out_dtype, int T, int F,
-                        cudaStream_t stream) {
+// zero (optional): a float32 buffer of zero_count values cleared on the side, for the product after the activation when
+// it sums partial results into its output.
+extern "C" int lp_xielu(const float* z, int ldz, const float* pq, void* out, int out_dtype, int T, int F, float* zero,
+                        long long zero_count, cudaStream_t stream) {
     if (T <= 0 || F <= 0) return 0;
     if (ldz < F) LP_REFUSE("xielu: rows of %d values for %d features", ldz, F);
     if (F % 4 == 0 && ldz % 4 == 0 && (((uintptr_t)z | (uintptr_t)out) & 15) == 0) {
         const long long n4 = (long long)T * (F / 4);
         long long blocks4 = (n4 + 255) / 256;
         if (blocks4 > 148 * 16) blocks4 = 148 * 16;
-        if (out_dtype == LP_F32) lp_launch(xielu_vec4_kernel<float>, (unsigned)blocks4, 256, 0, stream, z, ldz, pq, (float*)out, T, F);
+        if (out_dtype == LP_F32) lp_launch(xielu_vec4_kernel<float>, (unsigned)blocks4, 256, 0, stream, z, ldz, pq, (float*)out, T, F, zero, zero_count);
         else if (out_dtype == LP_BF16)
-            lp_launch(xielu_vec4_kernel<__nv_bfloat16>, (unsigned)blocks4, 256, 0, stream, z, ldz, pq, (__nv_bfloat16*)out, T, F);
+            lp_launch(xielu_vec4_kernel<__nv_bfloat16>, (unsigned)blocks4, 256, 0, stream, z, ldz, pq, (__nv_bfloat16*)out, T, F, zero, zero_count);
         else LP_REFUSE("xielu: output dtype code %d", out_dtype);
         return lp_check_launch("xielu");
     }
     const long long n = (long long)T * F;
     long long blocks = (n + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
-    if (out_dtype == LP_F32) lp_launch(xielu_kernel<float>, (unsigned)blocks, 256, 0, stream, z, ldz, pq, (float*)out, T, F);
+    if (out_dtype == LP_F32) lp_launch(xielu_kernel<float>, (unsigned)blocks, 256, 0, stream, z, ldz, pq, (float*)out, T, F, zero, zero_count);
     else if (out_dtype == LP_BF16)
-        lp_launch(xielu_kernel<__nv_bfloat16>, (unsigned)blocks, 256, 0, stream, z, ldz, pq, (__nv_bfloat16*)out, T, F);
+        lp_launch(xielu_kernel<__nv_bfloat16>, (unsigned)blocks, 256, 0, stream, z, ldz, pq, (__nv_bfloat16*)out, T, F, zero, zero_count);
     else LP_REFUSE("xielu: output dtype code %d", out_dtype);
     return lp_check_launch("xielu");
 }

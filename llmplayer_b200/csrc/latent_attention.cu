@@ -128,9 +128,11 @@ latent_heads_to_pages_kernel(const __nv_bfloat16* __restrict__ kv, const __nv_bf
 // out[t, h * dv + v] = heads[t, h * hd + v] * sigmoid(gate[t, h]): the first dv features of each head, gated.
 __global__ void __launch_bounds__(256)
 latent_gate_heads_kernel(const __nv_bfloat16* __restrict__ heads, const float* __restrict__ gate, int ldg,
-                         __nv_bfloat16* __restrict__ out, int T, int H, int hd, int dv) {
+                         __nv_bfloat16* __restrict__ out, int T, int H, int hd, int dv, float* __restrict__ zero,
+                         long long zero_count) {
     lp_grid_release();
     lp_grid_wait();
+    clear_on_the_side(zero, zero_count);
     const long long n = (long long)T * H * dv;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
         const long long th = i / dv;
@@ -382,12 +384,14 @@ latent_merge_kernel(const float* __restrict__ part, int shares, float* __restric
 template <typename TW, typename TOut>
 __global__ void __launch_bounds__(128)
 latent_expand_kernel(const float* __restrict__ part, int shares, const TW* __restrict__ uv,
-                     const float* __restrict__ gate, int ldg, TOut* __restrict__ out, int T, int H, int rank, int dv) {
+                     const float* __restrict__ gate, int ldg, TOut* __restrict__ out, int T, int H, int rank, int dv,
+                     float* __restrict__ zero, long long zero_count) {
     extern __shared__ float ls[];                         // [TOK_TILE][rank], then [TOK_TILE][shares] weights
     __shared__ float gs[TOK_TILE];
     float* ws = ls + TOK_TILE * rank;
     lp_grid_release();
     lp_grid_wait();
+    clear_on_the_side(zero, zero_count);
     const int t0 = blockIdx.x * TOK_TILE, h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nt = min(TOK_TILE, T - t0);
     const int width = rank + 2;
@@ -438,6 +442,56 @@ latent_expand_kernel(const float* __restrict__ part, int shares, const TW* __res
             const float s = lp_warp_sum(acc[i]);
             if (lane == 0 && i < nt) out[((long long)(t0 + i) * H + h) * dv + v] = lp_from_float<TOut>(s * gs[i]);
         }
+    }
+}
+
+// The same for a step of few tokens, one CTA per (token, head) row: the row's shares are merged by all threads,
+// then each warp forms value features of the row (lanes over the latent).
+template <typename TW, typename TOut>
+__global__ void __launch_bounds__(256)
+latent_expand_rows_kernel(const float* __restrict__ part, int shares, const TW* __restrict__ uv,
+                          const float* __restrict__ gate, int ldg, TOut* __restrict__ out, int H, int rank, int dv,
+                          float* __restrict__ zero, long long zero_count) {
+    extern __shared__ float ls[];                         // [rank] merged latent, then [shares] weights
+    float* ws = ls + rank;
+    lp_grid_release();
+    lp_grid_wait();
+    clear_on_the_side(zero, zero_count);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int row = blockIdx.x, t = row / H, h = row - t * H;
+    const int width = rank + 2;
+    const float* p = part + (long long)row * shares * width;
+    float M = -INFINITY;
+    for (int s = lane; s < shares; s += 32) M = fmaxf(M, p[s * width + rank]);
+    M = lp_warp_max(M);
+    float L = 0.f;
+    for (int s = lane; s < shares; s += 32) {
+        const float ms = p[s * width + rank];
+        L += ms == -INFINITY ? 0.f : p[s * width + rank + 1] * expf(ms - M);
+    }
+    L = lp_warp_sum(L);
+    const float inv = 1.0f / L;
+    if (warp == 0)
+        for (int s = lane; s < shares; s += 32) {
+            const float ms = p[s * width + rank];
+            ws[s] = ms == -INFINITY ? 0.f : expf(ms - M) * inv;
+        }
+    __syncthreads();
+    for (int r = tid; r < rank; r += blockDim.x) {
+        float acc = 0.f;
+#pragma unroll 8
+        for (int s = 0; s < shares; ++s) acc = fmaf(p[(long long)s * width + r], ws[s], acc);
+        ls[r] = acc;
+    }
+    __syncthreads();
+    const float g = gate ? 1.0f / (1.0f + expf(-gate[(long long)t * ldg + h])) : 1.0f;
+    for (int v = warp; v < dv; v += 8) {
+        const TW* w = uv + ((long long)h * dv + v) * rank;
+        float acc = 0.f;
+#pragma unroll 8
+        for (int r = lane; r < rank; r += 32) acc = fmaf(ls[r], lp_to_float(w[r]), acc);
+        acc = lp_warp_sum(acc);
+        if (lane == 0) out[(long long)row * dv + v] = lp_from_float<TOut>(acc * g);
     }
 }
 
@@ -553,10 +607,30 @@ extern "C" int lp_latent_merge(const float* part, int shares, float* out, int ro
 
 // part: as lp_latent_attend leaves it; uv: [H * dv, rank]; gate: float32 [T, ldg] with one value per head
 // (or null); out: [T, H * dv].
+// zero (optional): a float32 buffer cleared on the side. Steps of at most ROWS_FORM_TOKENS tokens take the form with one
+// CTA per (token, head) row.
+constexpr int ROWS_FORM_TOKENS = 64;
 extern "C" int lp_latent_expand(const float* part, int shares, const void* uv, int w_dtype, const float* gate, int ldg,
-                                void* out, int out_dtype, int T, int H, int rank, int dv, cudaStream_t stream) {
+                                void* out, int out_dtype, int T, int H, int rank, int dv, float* zero, long long zero_count,
+                                cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || H > 65535 || rank <= 0 || dv <= 0 || shares <= 0) LP_REFUSE("latent_expand: %d heads, rank %d, values of %d, %d shares", H, rank, dv, shares);
+    if (T <= ROWS_FORM_TOKENS) {
+        const size_t bytes = (size_t)(rank + shares) * sizeof(float);
+#define LP_LAUNCH_ROWS(TW, TOut)                                                                                     \
+    do {                                                                                                             \
+        if (grant_shared(latent_expand_rows_kernel<TW, TOut>, bytes, "latent_expand")) return -1;                    \
+        lp_launch(latent_expand_rows_kernel<TW, TOut>, T * H, 256, bytes, stream, part, shares, (const TW*)uv, gate,  \
+                  ldg, (TOut*)out, H, rank, dv, zero, zero_count);                                                   \
+    } while (0)
+        if (w_dtype == LP_F32 && out_dtype == LP_F32) LP_LAUNCH_ROWS(float, float);
+        else if (w_dtype == LP_BF16 && out_dtype == LP_BF16) LP_LAUNCH_ROWS(__nv_bfloat16, __nv_bfloat16);
+        else if (w_dtype == LP_BF16 && out_dtype == LP_F32) LP_LAUNCH_ROWS(__nv_bfloat16, float);
+        else if (w_dtype == LP_F32 && out_dtype == LP_BF16) LP_LAUNCH_ROWS(float, __nv_bfloat16);
+        else LP_REFUSE("latent_expand: dtype codes w=%d out=%d", w_dtype, out_dtype);
+#undef LP_LAUNCH_ROWS
+        return lp_check_launch("latent_expand");
+    }
     // few tokens: the value columns of a head are shared out over CTAs as well (each merges the shares itself)
     const int tiles = (T + TOK_TILE - 1) / TOK_TILE;
     int vparts = 1;
@@ -567,7 +641,7 @@ extern "C" int lp_latent_expand(const float* part, int shares, const void* uv, i
     do {                                                                                                          \
         if (grant_shared(latent_expand_kernel<TW, TOut>, smem, "latent_expand")) return -1;                       \
         lp_launch(latent_expand_kernel<TW, TOut>, grid, 128, smem, stream, part, shares, (const TW*)uv, gate, ldg, \
-                  (TOut*)out, T, H, rank, dv);                                                                    \
+                  (TOut*)out, T, H, rank, dv, zero, zero_count);                                                  \
     } while (0)
     if (w_dtype == LP_F32 && out_dtype == LP_F32) LP_LAUNCH_EXPAND(float, float);
     else if (w_dtype == LP_BF16 && out_dtype == LP_BF16) LP_LAUNCH_EXPAND(__nv_bfloat16, __nv_bfloat16);
@@ -594,13 +668,13 @@ extern "C" int lp_latent_heads_to_pages(const void* kv, const void* shared_part,
 }
 
 extern "C" int lp_latent_gate_heads(const void* heads, const float* gate, int ldg, void* out, int T, int H, int hd, int dv,
-                                    cudaStream_t stream) {
+                                    float* zero, long long zero_count, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || dv <= 0 || dv > hd) LP_REFUSE("latent_gate_heads: %d heads of %d, values of %d", H, hd, dv);
     const long long n = (long long)T * H * dv;
     long long blocks = (n + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     lp_launch(latent_gate_heads_kernel, (unsigned)blocks, 256, 0, stream, (const __nv_bfloat16*)heads, gate, ldg,
-              (__nv_bfloat16*)out, T, H, hd, dv);
+              (__nv_bfloat16*)out, T, H, hd, dv, zero, zero_count);
     return lp_check_launch("latent_gate_heads");
 }

@@ -57,7 +57,7 @@ constexpr int TB = 16;            // tokens per round of loads
 constexpr int SCAN_WHOLE = 0, SCAN_LOCAL = 1, SCAN_OUTPUT = 2;
 
 template <int KP, int VT, int KPT, int JT>
-__global__ void __launch_bounds__(VT / JT * KP, 3)
+__global__ void __launch_bounds__(VT / JT * KP)
 gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off, const float* __restrict__ decay,
                 float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ q_start,
                 float* __restrict__ out, int H, int dk, int dv, float q_scale, int mode, int chunks, int chunk,
@@ -185,9 +185,10 @@ gla_combine_kernel(float* __restrict__ state, const int* __restrict__ slots, con
 template <typename TOut>
 __global__ void __launch_bounds__(256)
 gla_finish_kernel(const float* __restrict__ o, const float* __restrict__ gain, float eps, const float* __restrict__ gate,
-                  int ldg, TOut* __restrict__ out, int T, int H, int dv) {
+                  int ldg, TOut* __restrict__ out, int T, int H, int dv, float* __restrict__ zero, long long zero_count) {
     lp_grid_release();
     lp_grid_wait();
+    clear_on_the_side(zero, zero_count);
     const int lane = threadIdx.x & 31;
     const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= (long long)T * H) return;
@@ -278,14 +279,14 @@ extern "C" int lp_gla_scan(const float* proj, int ld, int q_off, int k_off, int 
 }
 
 extern "C" int lp_gla_finish(const float* o, const float* gain, float eps, const float* gate, int ldg, void* out,
-                             int out_dtype, int T, int H, int dv, cudaStream_t stream) {
+                             int out_dtype, int T, int H, int dv, float* zero, long long zero_count, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || dv <= 0) LP_REFUSE("gla_finish: %d heads of %d", H, dv);
     const long long rows = (long long)T * H;
     const unsigned blocks = (unsigned)((rows + 7) / 8);
-    if (out_dtype == LP_F32) lp_launch(gla_finish_kernel<float>, blocks, 256, 0, stream, o, gain, eps, gate, ldg, (float*)out, T, H, dv);
+    if (out_dtype == LP_F32) lp_launch(gla_finish_kernel<float>, blocks, 256, 0, stream, o, gain, eps, gate, ldg, (float*)out, T, H, dv, zero, zero_count);
     else if (out_dtype == LP_BF16)
-        lp_launch(gla_finish_kernel<__nv_bfloat16>, blocks, 256, 0, stream, o, gain, eps, gate, ldg, (__nv_bfloat16*)out, T, H, dv);
+        lp_launch(gla_finish_kernel<__nv_bfloat16>, blocks, 256, 0, stream, o, gain, eps, gate, ldg, (__nv_bfloat16*)out, T, H, dv, zero, zero_count);
     else LP_REFUSE("gla_finish: output dtype code %d", out_dtype);
     return lp_check_launch("gla_finish");
 }

@@ -78,7 +78,7 @@ class Engine:
         torch.cuda.set_device(dev)
         runtime = Runtime(device=dev, dtype=opts.dtype, kernels=opts.kernels)
         model = Model(config.layout())
-        tensors = load_tensors(model_dir, model.tensor_specs())
+        tensors = load_tensors(model_dir, model.tensor_specs(), ignore=config.ignorable_tensors())
         model.load(tensors, runtime)
         del tensors
         limit = config.max_positions()

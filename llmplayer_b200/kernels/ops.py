@@ -25,7 +25,7 @@ _SIGNATURES = {
     "elementwise": {
         "lp_embed": [_P, _I, _P, _P, _I, _I, _F, _P],
         "lp_layernorm": [_P, _P, _P, _P, _I, _I, _I, _F, _P],
-        "lp_xielu": [_P, _I, _P, _P, _I, _I, _I, _P],
+        "lp_xielu": [_P, _I, _P, _P, _I, _I, _I, _P, ctypes.c_longlong, _P],
         "lp_gated_sum": [_P, _P, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P],
         "lp_rmsnorm": [_P, _P, _I, _P, _P, _P, _I, _I, _I, _F, _P, ctypes.c_longlong, _P],
         "lp_rope_cache_write": [_P, _I, _P, _P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
@@ -61,17 +61,17 @@ _SIGNATURES = {
         "lp_latent_prepare": [_P, _I, _I, _I, _P, _F, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P,
                               _I, _P],
         "lp_latent_heads_to_pages": [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
-        "lp_latent_gate_heads": [_P, _P, _I, _P, _I, _I, _I, _I, _P],
+        "lp_latent_gate_heads": [_P, _P, _I, _P, _I, _I, _I, _I, _P, ctypes.c_longlong, _P],
         "lp_latent_absorb": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _P],
         "lp_latent_attend_rows": [],
         "lp_latent_attend": [_P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
         "lp_latent_merge": [_P, _I, _P, _I, _I, _P],
-        "lp_latent_expand": [_P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P],
+        "lp_latent_expand": [_P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, ctypes.c_longlong, _P],
     },
     "linear_attention": {
         "lp_gla_decay": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _F, _P],
         "lp_gla_scan": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _P],
-        "lp_gla_finish": [_P, _P, _F, _P, _I, _P, _I, _I, _I, _I, _P],
+        "lp_gla_finish": [_P, _P, _F, _P, _I, _P, _I, _I, _I, _I, _P, ctypes.c_longlong, _P],
     },
     "host_loop": {
         "lp_decode_loop": [_P, _P, _P, _I, _I, _I, _P, _I, _I, _P, _P, _P, _P, _P],
@@ -413,9 +413,18 @@ def _slice(t: torch.Tensor, what: str):
     return t.data_ptr(), int(t.stride(0))
 
 
-def xielu(z: torch.Tensor, pq: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+def _clear_args(clear: Optional[torch.Tensor], what: str):
+    """(pointer, count) of a float32 buffer that a kernel zeroes on the side, or (None, 0)."""
+    if clear is None:
+        return None, 0
+    _want(clear, f"{what} clear", torch.float32)
+    return clear.data_ptr(), clear.numel()
+
+
+def xielu(z: torch.Tensor, pq: torch.Tensor, out: torch.Tensor, clear: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out = softplus(p) z^2 + z / 2 where z > 0, (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2 elsewhere;
-    ``z``: float32 [T, F] (may be a column slice), ``pq``: float32 [2] on the device."""
+    ``z``: float32 [T, F] (may be a column slice), ``pq``: float32 [2] on the device. ``clear``: a float32 buffer zeroed
+    on the side (for the product after it, when that sums partial results into its output)."""
     zp, ldz = _slice(z, "xielu z")
     _want(pq, "xielu numbers", torch.float32, 1)
     _want(out, "xielu out", ndim=2)
@@ -423,7 +432,7 @@ def xielu(z: torch.Tensor, pq: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         raise KernelError(f"xielu: z {tuple(z.shape)}, out {tuple(out.shape)}, {pq.numel()} numbers")
     lib = library("elementwise")
     _check(lib, lib.lp_xielu(zp, ldz, pq.data_ptr(), out.data_ptr(), _code(out, "xielu out"), z.shape[0], z.shape[1],
-                             _stream()))
+                             *_clear_args(clear, "xielu"), _stream()))
     return out
 
 
@@ -1071,7 +1080,7 @@ def latent_heads_to_pages(kv: torch.Tensor, shared_part: torch.Tensor, positions
 
 
 def latent_gate_heads(heads: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, *, num_heads: int,
-                      head_dim: int, value_dim: int) -> torch.Tensor:
+                      head_dim: int, value_dim: int, clear: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[t, h * dv + v] = heads[t, h * hd + v] * sigmoid(gate[t, h]) (bfloat16; ``gate`` float32 [T, H], may be a
     column slice, or None)."""
     _want(heads, "latent_gate_heads heads", torch.bfloat16, 2)
@@ -1086,7 +1095,7 @@ def latent_gate_heads(heads: torch.Tensor, gate: Optional[torch.Tensor], out: to
             raise KernelError(f"latent_gate_heads: gate {tuple(gate.shape)} for {T} tokens and {num_heads} heads")
     lib = library("latent_attention")
     _check(lib, lib.lp_latent_gate_heads(heads.data_ptr(), gp, ldg, out.data_ptr(), T, num_heads, head_dim, value_dim,
-                                         _stream()))
+                                         *_clear_args(clear, "latent_gate_heads"), _stream()))
     return out
 
 
@@ -1140,6 +1149,9 @@ def latent_attend(q_abs: torch.Tensor, pages: torch.Tensor, page_table: torch.Te
     return partials
 
 
+LATENT_ROWS_FORM_TOKENS = 64      # up to here latent_expand runs one CTA per (token, head) row and merges the shares itself
+
+
 def latent_merge(partials: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """The shares of every (token, head) row of ``partials`` [T, H, shares, rank + 2] merged into one share
     ``out`` [T, H, 1, rank + 2] whose sum of weights is one."""
@@ -1154,7 +1166,7 @@ def latent_merge(partials: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
 
 
 def latent_expand(partials: torch.Tensor, v_up: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, *,
-                  value_dim: int) -> torch.Tensor:
+                  value_dim: int, clear: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[t, h * dv + v] = sigmoid(gate[t, h]) * (v_up[h] latent[t, h])[v], the latent being the merge of the
     shares in ``partials``; ``gate``: float32 [T, H] (may be a column slice) or None."""
     _want(partials, "latent_expand partials", torch.float32, 4)
@@ -1171,7 +1183,8 @@ def latent_expand(partials: torch.Tensor, v_up: torch.Tensor, gate: Optional[tor
             raise KernelError(f"latent_expand: gate {tuple(gate.shape)} for {T} tokens and {H} heads")
     lib = library("latent_attention")
     _check(lib, lib.lp_latent_expand(partials.data_ptr(), shares, v_up.data_ptr(), _code(v_up, "latent_expand v_up"), gp, ldg,
-                                     out.data_ptr(), _code(out, "latent_expand out"), T, H, rank, value_dim, _stream()))
+                                     out.data_ptr(), _code(out, "latent_expand out"), T, H, rank, value_dim,
+                                     *_clear_args(clear, "latent_expand"), _stream()))
     return out
 
 
@@ -1238,7 +1251,7 @@ def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torc
 
 
 def gla_finish(o: torch.Tensor, gain: torch.Tensor, eps: float, gate: Optional[torch.Tensor], out: torch.Tensor, *,
-               num_heads: int, value_dim: int) -> torch.Tensor:
+               num_heads: int, value_dim: int, clear: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[t, h] = rmsnorm(o[t, h]) * gain * silu(gate[t, h]) per head of ``value_dim`` values; ``gate``: float32
     [T, H * dv] (may be a column slice) or None."""
     _want(o, "gla_finish o", torch.float32, 2)
@@ -1254,7 +1267,8 @@ def gla_finish(o: torch.Tensor, gain: torch.Tensor, eps: float, gate: Optional[t
             raise KernelError(f"gla_finish: gate {tuple(gate.shape)} does not match o {tuple(o.shape)}")
     lib = library("linear_attention")
     _check(lib, lib.lp_gla_finish(o.data_ptr(), gain.data_ptr(), float(eps), gp, ldg, out.data_ptr(),
-                                  _code(out, "gla_finish out"), T, num_heads, value_dim, _stream()))
+                                  _code(out, "gla_finish out"), T, num_heads, value_dim, *_clear_args(clear, "gla_finish"),
+                                  _stream()))
     return out
 
 

@@ -109,8 +109,14 @@ class XIELUFeedForward(Part):
         """``z``: the float32 sums up x [T, F] (may be a column slice); writes down(act(z)) to ``out`` float32 [T, d]."""
         from ..kernels import ops
         h = ctx.buffer("ffn_hidden", (z.shape[0], self.spec.intermediate_size), self.runtime.act_dtype)
+        # a down product that sums partial results into `out` wants it zero: the activation clears it on the side
+        clear = self.down.sums_into(ctx, z.shape[0], "ffn_out", ops.STORE)
+        if clear is not None and clear.data_ptr() != out.data_ptr():
+            clear = None
         with ops.section("ffn.act"):
-            ops.xielu(z, self.numbers, h)
+            ops.xielu(z, self.numbers, h, clear=clear)
+        if clear is not None:
+            ctx.note_cleared()
         with ops.section("ffn.down"):
             self.down.store(h, out, ctx)
         return out

@@ -112,15 +112,25 @@ class LatentAttention(Part):
                               kv_rank=rank, scale=s.scale)
         o = ctx.buffer("attn_out", (T, H * dv), rt.act_dtype)
         gate = proj[:, gate_off:gate_off + H] if s.out_gate is not None else None
+        clear = self._out_to_clear(ctx, T, out)
         with ops.section("attention.values"):
-            if shares > 2:
-                # many shares: one CTA per row merges them, so that the value map's CTAs need not each do it
+            if shares > 2 and T > ops.LATENT_ROWS_FORM_TOKENS:
+                # many shares in a long step: one CTA per row merges them, so that the value map's CTAs (a tile of
+                # tokens each) need not each do it; a short step merges inside the value map's kernel, a CTA per row
                 merged = ctx.buffer("latent_merged", (T, H, 1, rank + 2), torch.float32)
                 partials = ops.latent_merge(partials, merged)
-            ops.latent_expand(partials, self.v_up, gate, o, value_dim=dv)
+            ops.latent_expand(partials, self.v_up, gate, o, value_dim=dv, clear=clear)
+        if clear is not None:
+            ctx.note_cleared()
         with ops.section("attention.out"):
             self.out.store(o, out, ctx)
         return out
+
+    def _out_to_clear(self, ctx, tokens: int, out: torch.Tensor):
+        """``out`` if the output product will sum partial results into it (the kernel before it then clears it on the
+        side), else None."""
+        clear = self.out.sums_into(ctx, tokens, "mixer_out", ops.STORE)
+        return clear if clear is not None and clear.data_ptr() == out.data_ptr() else None
 
     # ------------------------------------------------------------------ prompts: every head's keys and values outright
     HEADS_MIN_TOKENS = 48
@@ -177,8 +187,11 @@ class LatentAttention(Part):
                                   num_kv_heads=H, head_dim=hd, scale=s.scale, window=None)
         o = ctx.buffer("attn_out", (T, H * dv), torch.bfloat16)
         gate = proj[:, gate_off:gate_off + H] if s.out_gate is not None else None
+        clear = self._out_to_clear(ctx, T, out)
         with ops.section("attention.values"):
-            ops.latent_gate_heads(heads, gate, o, num_heads=H, head_dim=hd, value_dim=dv)
+            ops.latent_gate_heads(heads, gate, o, num_heads=H, head_dim=hd, value_dim=dv, clear=clear)
+        if clear is not None:
+            ctx.note_cleared()
         with ops.section("attention.out"):
             self.out.store(o, out, ctx)
         return out

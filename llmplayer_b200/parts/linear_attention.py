@@ -98,8 +98,15 @@ class GatedLinearAttention(Part):
             ops.gla_scan(proj, q_off, k_off, v_off, decay, cache.rows, ctx.slots, ctx.q_start, raw, num_heads=H,
                          key_dim=dk, value_dim=dv, q_scale=float(dk) ** -0.5, max_new=ctx.max_new, scratch=ctx.buffer)
         o = ctx.buffer("attn_out", (T, H * dv), rt.act_dtype)
+        # an output product that sums partial results into `out` wants it zero: the kernel before it clears it
+        clear = self.out.sums_into(ctx, T, "mixer_out", ops.STORE)
+        if clear is not None and clear.data_ptr() != out.data_ptr():
+            clear = None
         with ops.section("recurrence.norm"):
-            ops.gla_finish(raw, self.out_gain, s.norm_eps, proj[:, g_off:g_off + H * dv], o, num_heads=H, value_dim=dv)
+            ops.gla_finish(raw, self.out_gain, s.norm_eps, proj[:, g_off:g_off + H * dv], o, num_heads=H, value_dim=dv,
+                           clear=clear)
+        if clear is not None:
+            ctx.note_cleared()
         with ops.section("recurrence.out"):
             self.out.store(o, out, ctx)
         return out

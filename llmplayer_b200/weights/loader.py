@@ -28,7 +28,8 @@ def held_dtype(stored: str, kind: str) -> torch.dtype:
     return torch.bfloat16 if stored == "BF16" else torch.float32
 
 
-def load_tensors(model_dir: str, expected: Mapping[str, TensorSpec]) -> Dict[str, torch.Tensor]:
+def load_tensors(model_dir: str, expected: Mapping[str, TensorSpec], ignore=()) -> Dict[str, torch.Tensor]:
+    """``ignore``: names that a file may hold although the layout does not use them (they are not loaded)."""
     owners = open_model_files(model_dir)
     try:
         missing, wrong = [], []
@@ -44,7 +45,8 @@ def load_tensors(model_dir: str, expected: Mapping[str, TensorSpec]) -> Dict[str
                 wrong.append(f"{name}: expected an integer table, file has dtype {dtype}")
             elif spec.kind in (MATRIX, GAIN, BIAS) and dtype not in _FLOATS:
                 wrong.append(f"{name}: expected floating-point values, file has dtype {dtype}")
-        unexpected = sorted(n for n in owners if n not in expected)
+        ignore = set(ignore)
+        unexpected = sorted(n for n in owners if n not in expected and n not in ignore)
         if missing or wrong or unexpected:
             lines = [f"the tensors of {model_dir!r} do not fit the configuration:"]
             if missing:

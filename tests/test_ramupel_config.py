@@ -76,6 +76,17 @@ def test_a_size_left_to_the_file_is_accepted_and_a_mismatch_is_reported(tmp_path
     with pytest.raises(WeightError, match=r"l1.mix.a2: expected shape \[40, 'any'\]"):
         load_tensors(out, expected_tensors(cfg.layout()))
     assert json.load(open(os.path.join(out, "config.json")))["architecture"] == "Ramupel"
+    # a gate for the feed-forward that layer 1 does not have is passed over, anything else unexpected is reported
+    tensors["l1.mix.a2"] = torch.zeros(40, 7, dtype=torch.bfloat16)
+    tensors["l1.rg2"] = torch.zeros(88, 88, dtype=torch.bfloat16)
+    tensors["l1.rg2.b"] = torch.zeros(88, dtype=torch.bfloat16)
+    write_safetensors(path, tensors)
+    loaded = load_tensors(out, expected_tensors(cfg.layout()), ignore=cfg.ignorable_tensors())
+    assert "l1.rg2" not in loaded and cfg.ignorable_tensors() == ("l1.rg2", "l1.rg2.b")
+    tensors["l0.extra"] = torch.zeros(3, dtype=torch.bfloat16)
+    write_safetensors(path, tensors)
+    with pytest.raises(WeightError, match=r"unexpected \(1\): l0.extra"):
+        load_tensors(out, expected_tensors(cfg.layout()), ignore=cfg.ignorable_tensors())
 
 
 def test_cache_groups_rows_and_states():
