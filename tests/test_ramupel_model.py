@@ -25,7 +25,8 @@ def vocab(name):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name,length", [("small", 1), ("small", 2), ("small", 97), ("small", 300), ("wide", 33), ("wide", 200), ("wide", 321)])
+@pytest.mark.parametrize("name,length", [("small", 1), ("small", 2), ("small", 97), ("small", 300), ("wide", 33), ("wide", 200), ("wide", 321),
+                                         ("ragged", 3), ("ragged", 270)])
 def test_whole_sequence(tmp_path, name, length, dtype):
     from llmplayer_b200 import Engine
     model_dir = make_model(tmp_path, name, dtype)
@@ -39,7 +40,7 @@ def test_whole_sequence(tmp_path, name, length, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["small", "wide"])
+@pytest.mark.parametrize("name", ["small", "wide", "ragged"])
 def test_prompt_then_token_by_token(tmp_path, name, dtype):
     """Most of a sequence in one step, the rest one token at a time across a page's border (position 128) and
     two borders of key blocks; every decoded position against the whole-sequence plain implementation."""
@@ -78,7 +79,7 @@ def test_portions_of_a_prompt(tmp_path, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["small", "wide"])
+@pytest.mark.parametrize("name", ["small", "wide", "ragged"])
 def test_unequal_batches_and_reuse(tmp_path, name, dtype):
     """Requests of unequal lengths in one batch, decoded together while the shorter ones end; then new requests
     in the slots and pages that were given back (their state must start at zero); each against itself alone."""
