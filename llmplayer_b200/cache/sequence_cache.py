@@ -2,7 +2,7 @@
 layers with equal needs, and a per-sequence state area of fixed size.
 
 What a run of a layer needs is said by its mixer (a :class:`KVRequest`, a
-:class:`StateRequest` or nothing). Runs with the same key/value geometry and
+:class:`StateRequest`, a tuple of those for several blocks, or nothing). Runs with the same key/value geometry and
 window share one :class:`KVGroup` — one storage tensor and one page map —
 so layers that keep all keys and layers that keep a window of them have storage
 of their own. State requests get one row per slot each, zeroed when the slot is
@@ -85,10 +85,12 @@ class KVView:
 
 
 class StateView:
-    """What a run with fixed-size state sees: one row per slot."""
+    """What a run with fixed-size state sees: one row per slot (``rows``); a run that asked for several blocks
+    (a tuple of :class:`StateRequest`) finds them all in ``blocks``, in the order it asked."""
 
-    def __init__(self, rows: torch.Tensor):
+    def __init__(self, rows: torch.Tensor, blocks: Optional[Sequence[torch.Tensor]] = None):
         self.rows = rows
+        self.blocks = list(blocks) if blocks is not None else [rows]
 
 
 class SequenceCache:
@@ -118,9 +120,11 @@ class SequenceCache:
         self._state_rows: List[torch.Tensor] = []
         for run, req in enumerate(requests):
             if isinstance(req, StateRequest):
-                rows = torch.zeros((self.max_slots,) + tuple(req.shape), dtype=req.dtype, device=device)
-                self._state_rows.append(rows)
-                self._views[run] = StateView(rows)
+                req = (req,)
+            if isinstance(req, tuple) and req and all(isinstance(r, StateRequest) for r in req):
+                blocks = [torch.zeros((self.max_slots,) + tuple(r.shape), dtype=r.dtype, device=device) for r in req]
+                self._state_rows.extend(blocks)
+                self._views[run] = StateView(blocks[0], blocks)
             elif req is not None and not isinstance(req, (KVRequest, RowsRequest)):
                 raise CacheError(f"run {run}: unknown cache request {req!r}")
 

@@ -140,6 +140,28 @@ constexpr int HEAD_ROWS = 8;       // query heads per unit (a key/value head wit
 // whose share holds the new token's position rotates the new key, writes key and value into the cache
 // and into its own shared-memory copy of that page. The last CTA of a (sequence, kv head) to finish
 // merges the shares (a counter per group, zero before the launch and zero again after it).
+// What may shape a score besides the scale. A cap: score <- cap * tanh(score / cap) (cap_log2 = cap * log2(e),
+// scale_over_cap = scale / cap; cap_log2 == 0: scores are not capped). Sinks (float32 [H], natural units, or null): a
+// learned logit per head that enters the softmax's denominator once and has neither key nor value.
+struct ScoreExtras {
+    float cap_log2;
+    float scale_over_cap;
+    const float* sinks;
+};
+// tanh from the hardware's exp2 and a fast division: absolute error of about 1e-7
+__device__ __forceinline__ float lp_tanh_exp2(float x) {
+    const float e = exp2f(x * 2.885390081777927f);
+    return 1.0f - __fdividef(2.0f, e + 1.0f);
+}
+// a raw dot product -> the score in log2 units
+__device__ __forceinline__ float shaped_score(float raw, float scale_log2, const ScoreExtras& x) {
+    return x.cap_log2 > 0.f ? x.cap_log2 * lp_tanh_exp2(raw * x.scale_over_cap) : raw * scale_log2;
+}
+// the denominator's share of a head's sink, relative to the maximum m (log2 units)
+__device__ __forceinline__ float sink_term(const ScoreExtras& x, int head, float m) {
+    return x.sinks ? exp2f(x.sinks[head] * 1.4426950408889634f - m) : 0.f;
+}
+
 struct FusedDecodeArgs {
     const float* qkv;          // [B, ld]
     int ld;
@@ -152,6 +174,7 @@ struct FusedDecodeArgs {
     const float* row_sumsq;
     float norm_eps;
     int norm_width;
+    ScoreExtras score;         // zero: plain scaled scores
 };
 
 // The same in two steps, for callers that want the loads of several elements in flight before they combine them.
@@ -467,8 +490,10 @@ __device__ __forceinline__ void attention_decode_unit(
                 }
                 const int key_a = key_base + key0 + g8, key_b = key_a + 8;
                 const bool out_a = key_a > pos || key_a < lo, out_b = key_b > pos || key_b < lo;
-                s[0] = out_a ? NEG_BIG : s[0] * scale_log2; s[1] = out_a ? NEG_BIG : s[1] * scale_log2;
-                s[2] = out_b ? NEG_BIG : s[2] * scale_log2; s[3] = out_b ? NEG_BIG : s[3] * scale_log2;
+                s[0] = out_a ? NEG_BIG : shaped_score(s[0], scale_log2, fused.score);
+                s[1] = out_a ? NEG_BIG : shaped_score(s[1], scale_log2, fused.score);
+                s[2] = out_b ? NEG_BIG : shaped_score(s[2], scale_log2, fused.score);
+                s[3] = out_b ? NEG_BIG : shaped_score(s[3], scale_log2, fused.score);
                 float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);        // over the 16 keys: the lanes of equal t4
 #pragma unroll
                 for (int sh = 4; sh < 32; sh <<= 1) {
@@ -562,6 +587,7 @@ __device__ __forceinline__ void attention_decode_unit(
             l += sm_l[w * HEAD_ROWS + r] * f;
         }
         if ((FUSED ? shares : num_splits) == 1) {   // the only share: this is the result
+            if (l > 0.f) l += sink_term(fused.score, head0 + r, m);
             out[((size_t)b * H + head0 + r) * hd + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
         } else {
             const size_t slot = ((size_t)b * H + head0 + r) * num_splits + split;
@@ -614,6 +640,7 @@ __device__ __forceinline__ void attention_decode_unit(
                         }
                     }
                 }
+                if (l > 0.f) l += sink_term(fused.score, head0 + r, m);
                 out[((size_t)b * H + head0 + r) * hd + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
             }
         }

@@ -33,7 +33,7 @@ __global__ void __launch_bounds__(128)
 attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
                          const __nv_bfloat16* __restrict__ pages, const int* __restrict__ page_table, int pt_stride,
                          const int* __restrict__ q_start, const int* __restrict__ kv_len, int H, int G, int hd,
-                         float scale_log2, int window) {
+                         float scale_log2, int window, ScoreExtras extras) {
     constexpr int KSTEPS = HD_MAX / 16;
     extern __shared__ __align__(128) uint8_t smem[];
     lp_grid_release();
@@ -108,7 +108,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
                 for (int e = 0; e < 4; ++e) {
                     const int key = key_base + nt * 8 + (lane & 3) * 2 + (e & 1);
                     const int pos = (e < 2) ? pos_lo : pos_hi;
-                    float v = s[nt][e] * scale_log2;
+                    float v = shaped_score(s[nt][e], scale_log2, extras);
                     if (edge && (key > pos || (window > 0 && key <= pos - window))) v = NEG_BIG;
                     s[nt][e] = v;
                     if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
@@ -144,6 +144,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     cp_async_wait<0>();
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    l_lo += sink_term(extras, h, m_lo); l_hi += sink_term(extras, h, m_hi);
     const float inv_lo = 1.0f / l_lo, inv_hi = 1.0f / l_hi;
 #pragma unroll
     for (int dt = 0; dt < KSTEPS * 2; ++dt) {
@@ -169,7 +170,7 @@ __global__ void __launch_bounds__(ROWS * 2)
 attention_prefill_exact_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
                                const __nv_bfloat16* __restrict__ pages, const int* __restrict__ page_table,
                                int pt_stride, const int* __restrict__ q_start, const int* __restrict__ kv_len, int H,
-                               int G, float scale_log2, int window) {
+                               int G, float scale_log2_arg, int window, ScoreExtras extras) {
     constexpr int KSTEPS = HD / 16;
     constexpr int ROW = HD * 2;
     constexpr int TILE = PAGE * ROW;                  // bytes of a K (or V) tile
@@ -225,6 +226,8 @@ attention_prefill_exact_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat1
 #pragma unroll
     for (int i = 0; i < KSTEPS * 2; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m_lo = NEG_BIG, m_hi = NEG_BIG, l_lo = 0.f, l_hi = 0.f;      // maxima in scaled log2 units
+    const bool capped = extras.cap_log2 > 0.f;
+    const float scale_log2 = capped ? 1.0f : scale_log2_arg;
 
     load_page(smem, pages, table[page_lo], G, g, HD, tid, ROWS * 2);
     cp_async_commit();
@@ -252,6 +255,12 @@ attention_prefill_exact_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat1
                     mma_bf16(s[ks * 2], qf[kk], b0, b1);
                     mma_bf16(s[ks * 2 + 1], qf[kk], b2, b3);
                 }
+            }
+            if (capped) {                 // capped scores are formed here, in log2 units; the scale below is then 1
+#pragma unroll
+                for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) s[nt][e] = shaped_score(s[nt][e], scale_log2_arg, extras);
             }
             const bool edge = key_base + PAGE - 1 > warp_first_pos ||
                               (window > 0 && key_base <= warp_last_pos - window);
@@ -309,6 +318,7 @@ attention_prefill_exact_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat1
     cp_async_wait<0>();
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    l_lo += sink_term(extras, h, m_lo); l_hi += sink_term(extras, h, m_hi);
     const float inv_lo = 1.0f / l_lo, inv_hi = 1.0f / l_hi;
 #pragma unroll
     for (int dt = 0; dt < KSTEPS * 2; ++dt) {
@@ -368,7 +378,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const __
 
 // out[b][head][:] = sum_s part_o * 2^(m_s - m*) / sum_s l_s * 2^(m_s - m*); grid: (H, B), hd threads (<= 256).
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                       __nv_bfloat16* __restrict__ out, int H, int hd, int num_splits) {
+                                       __nv_bfloat16* __restrict__ out, int H, int hd, int num_splits,
+                                       ScoreExtras extras) {
     lp_grid_release();
     lp_grid_wait();
     const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
@@ -384,6 +395,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
             if (d < hd) acc += part_o[(base + s) * hd + d] * f;
         }
     }
+    if (l > 0.f) l += sink_term(extras, h, m);
     if (d < hd) out[((size_t)b * H + h) * hd + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
 }
 
@@ -415,14 +427,27 @@ int check_geometry(const char* what, int H, int G, int hd) {
     return 0;
 }
 
+// softcap > 0: scores are capped at it; sinks: float32 [H] or null (see ScoreExtras)
+static ScoreExtras make_extras(float scale, float softcap, const float* sinks) {
+    ScoreExtras x{};
+    if (softcap > 0.f) {
+        x.cap_log2 = softcap * 1.4426950408889634f;
+        x.scale_over_cap = scale / softcap;
+    }
+    x.sinks = sinks;
+    return x;
+}
+
 }  // namespace
 
 // q, out: [T, H, hd] bf16; pages: [num_pages, 2, G, 64, hd] bf16; q_start: [B+1]; kv_len: [B] (after the step).
 // max_new: the largest number of new tokens of any sequence of the step.
 extern "C" int lp_attention_prefill(const void* q, void* out, const void* pages, const int* page_table, int pt_stride,
                                     const int* q_start, const int* kv_len, int B, int max_new, int H, int G, int hd,
-                                    int page_size, float scale, int window, cudaStream_t stream) {
+                                    int page_size, float scale, int window, float softcap, const float* sinks,
+                                    cudaStream_t stream) {
     if (B <= 0 || max_new <= 0) return 0;
+    const ScoreExtras extras = make_extras(scale, softcap, sinks);
     int rc = check_geometry("attention_prefill", H, G, hd);
     if (rc) return rc;
     if (page_size != PAGE) LP_REFUSE("attention_prefill: pages of %d positions (built for %d)", page_size, PAGE);
@@ -436,7 +461,7 @@ extern "C" int lp_attention_prefill(const void* q, void* out, const void* pages,
         if (rc) return rc;                                                                                       \
         lp_launch(attention_prefill_kernel<HDM>, grid, 128, smem, stream,                                        \
             (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)pages, page_table, pt_stride,     \
-            q_start, kv_len, H, G, hd, scale_log2, window);                                                      \
+            q_start, kv_len, H, G, hd, scale_log2, window, extras);                                              \
     } while (0)
 #define LP_PREFILL_EXACT(HD, ROWS)                                                                               \
     do {                                                                                                         \
@@ -445,7 +470,7 @@ extern "C" int lp_attention_prefill(const void* q, void* out, const void* pages,
         dim3 grid_exact((max_new + ROWS - 1) / ROWS, H, B);                                                      \
         lp_launch(attention_prefill_exact_kernel<HD, ROWS>, grid_exact, ROWS * 2, smem, stream,                  \
                   (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)pages, page_table,         \
-                  pt_stride, q_start, kv_len, H, G, scale_log2, window);                                         \
+                  pt_stride, q_start, kv_len, H, G, scale_log2, window, extras);                                 \
     } while (0)
     // long prompts: 128 query rows share each page of keys; short ones keep 64 rows for more CTAs
     const bool tall = (long long)((max_new + 127) / 128) * H * B >= 8LL * lp_sm_count();
@@ -473,8 +498,10 @@ extern "C" long long lp_attention_decode_scratch(int B, int H, int hd, int num_s
 static int attention_decode_launch(const void* q, void* out, const void* pages, const int* page_table, int pt_stride,
                                    const int* kv_len, float* scratch, int B, int H, int G, int hd, int page_size,
                                    float scale, int window, int pages_per_split, int num_splits, int min_share_pages,
-                                   cudaStream_t stream) {
+                                   float softcap, const float* sinks, cudaStream_t stream) {
     if (B <= 0) return 0;
+    FusedDecodeArgs plain_args{};
+    plain_args.score = make_extras(scale, softcap, sinks);
     int rc = check_geometry("attention_decode", H, G, hd);
     if (rc) return rc;
     if (page_size != PAGE) LP_REFUSE("attention_decode: pages of %d positions (built for %d)", page_size, PAGE);
@@ -495,7 +522,7 @@ static int attention_decode_launch(const void* q, void* out, const void* pages, 
         lp_launch(attention_decode_kernel<HDM, false, EXACT, 3>, grid, 128, smem, stream,                           \
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, page_table, pt_stride, kv_len, part_o, part_ml, \
             (__nv_bfloat16*)out, H, G, hd, scale_log2, window, pages_per_split, num_splits, min_share_pages,     \
-            head_groups, FusedDecodeArgs{});                                                                     \
+            head_groups, plain_args);                                                                            \
     } while (0)
     if (hd == 64) LP_DECODE(64, 64); else if (hd == 128) LP_DECODE(128, 128);
     else if (hd <= 64) LP_DECODE(64, 0); else if (hd <= 128) LP_DECODE(128, 0); else LP_DECODE(256, 0);
@@ -503,25 +530,26 @@ static int attention_decode_launch(const void* q, void* out, const void* pages, 
     rc = lp_check_launch("attention_decode");
     if (rc || num_splits == 1) return rc;
     lp_launch(attention_merge_kernel, dim3(H, B), hd <= 32 ? 32 : (hd + 31) / 32 * 32, 0, stream,
-              (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, H, hd, num_splits);
+              (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, H, hd, num_splits, plain_args.score);
     return lp_check_launch("attention_merge");
 }
 
 extern "C" int lp_attention_decode(const void* q, void* out, const void* pages, const int* page_table, int pt_stride,
                                    const int* kv_len, float* scratch, int B, int H, int G, int hd, int page_size,
-                                   float scale, int window, int pages_per_split, int num_splits,
-                                   cudaStream_t stream) {
+                                   float scale, int window, int pages_per_split, int num_splits, float softcap,
+                                   const float* sinks, cudaStream_t stream) {
     return attention_decode_launch(q, out, pages, page_table, pt_stride, kv_len, scratch, B, H, G, hd, page_size, scale,
-                                   window, pages_per_split, num_splits, 0, stream);
+                                   window, pages_per_split, num_splits, 0, softcap, sinks, stream);
 }
 
 extern "C" int lp_attention_decode_fitted(const void* q, void* out, const void* pages, const int* page_table,
                                           int pt_stride, const int* kv_len, float* scratch, int B, int H, int G, int hd,
                                           int page_size, float scale, int window, int num_splits, int min_share_pages,
-                                          cudaStream_t stream) {
+                                          float softcap, const float* sinks, cudaStream_t stream) {
     if (min_share_pages <= 0) LP_REFUSE("attention_decode_fitted: shares of at least %d pages", min_share_pages);
     return attention_decode_launch(q, out, pages, page_table, pt_stride, kv_len, scratch, B, H, G, hd, page_size, scale,
-                                   window, pt_stride > 0 ? pt_stride : 1, num_splits, min_share_pages, stream);
+                                   window, pt_stride > 0 ? pt_stride : 1, num_splits, min_share_pages, softcap, sinks,
+                                   stream);
 }
 
 // Decode attention that starts from the fused projection output: rotation of queries and of the new key,
@@ -649,5 +677,5 @@ extern "C" int lp_attention_decode_noalloc(const void* q, void* out, const void*
         lp_decode_static_address[device] = address;
     }
     return lp_attention_decode(q, out, pages, page_table, pt_stride, kv_len, lp_decode_static_address[device], B, H, G,
-                               hd, page_size, scale, window, pages_per_split, num_splits, stream);
+                               hd, page_size, scale, window, pages_per_split, num_splits, 0.f, nullptr, stream);
 }

@@ -22,7 +22,7 @@ __global__ void __launch_bounds__(KB)
 attention_plain_kernel(const TQ* __restrict__ q, TQ* __restrict__ out, const TKV* __restrict__ pages,
                        const int* __restrict__ page_table, int pt_stride, const int* __restrict__ seq_ids,
                        const int* __restrict__ positions, int H, int G, int hd, int page_size, float scale,
-                       int window) {
+                       int window, float softcap, const float* __restrict__ sinks) {
     __shared__ float qs[MAX_HD];
     __shared__ float prob[KB];
     __shared__ long long row_off[KB];
@@ -54,6 +54,7 @@ attention_plain_kernel(const TQ* __restrict__ q, TQ* __restrict__ out, const TKV
             float dot = 0.f;
             for (int i = 0; i < hd; ++i) dot = fmaf(qs[i], lp_to_float(kr[i]), dot);
             sc = dot * scale;
+            if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);
         }
         const float cmax = lp_block_max(sc, scratch);
         const float m_new = fmaxf(m, cmax);
@@ -78,6 +79,15 @@ attention_plain_kernel(const TQ* __restrict__ q, TQ* __restrict__ out, const TKV
         m = m_new;
         __syncthreads();
     }
+    // a sink: a learned logit per head that takes part in the softmax's denominator only, once
+    if (sinks) {
+        const float sk = sinks[h];
+        const float m_new = fmaxf(m, sk);
+        const float alpha = expf(m - m_new);
+        l = l * alpha + expf(sk - m_new);
+        acc0 *= alpha;
+        acc1 *= alpha;
+    }
     const float inv = 1.0f / l;
     TQ* o = out + ((long long)t * H + h) * hd;
     if (tid < hd) o[tid] = lp_from_float<TQ>(acc0 * inv);
@@ -87,11 +97,12 @@ attention_plain_kernel(const TQ* __restrict__ q, TQ* __restrict__ out, const TKV
 }  // namespace
 
 // q, out: [T, H, hd]; pages: [num_pages, 2, G, page_size, hd]; page_table: [B, pt_stride];
-// seq_ids, positions: [T]. window <= 0: all keys up to the query's position.
+// seq_ids, positions: [T]. window <= 0: all keys up to the query's position. softcap > 0: a score s becomes
+// softcap * tanh(s / softcap) after the scale. sinks (optional): float32 [H], see the kernel.
 extern "C" int lp_attention_plain(const void* q, void* out, int q_dtype, const void* pages, int kv_dtype,
                                   const int* page_table, int pt_stride, const int* seq_ids, const int* positions,
                                   int T, int H, int G, int hd, int page_size, float scale, int window,
-                                  cudaStream_t stream) {
+                                  float softcap, const float* sinks, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G) LP_REFUSE("attention_plain: %d query heads over %d key heads", H, G);
     if (hd <= 0 || hd > MAX_HD) LP_REFUSE("attention_plain: head size %d (supported: 1..%d)", hd, MAX_HD);
@@ -101,7 +112,7 @@ extern "C" int lp_attention_plain(const void* q, void* out, int q_dtype, const v
 #define LP_LAUNCH_ATT(TQ, TKV)                                                                                 \
     attention_plain_kernel<TQ, TKV><<<grid, KB, 0, stream>>>((const TQ*)q, (TQ*)out, (const TKV*)pages,          \
                                                              page_table, pt_stride, seq_ids, positions, H, G,  \
-                                                             hd, page_size, scale, window)
+                                                             hd, page_size, scale, window, softcap, sinks)
     if (q_dtype == LP_F32 && kv_dtype == LP_F32) LP_LAUNCH_ATT(float, float);
     else if (q_dtype == LP_BF16 && kv_dtype == LP_BF16) LP_LAUNCH_ATT(__nv_bfloat16, __nv_bfloat16);
     else if (q_dtype == LP_F32 && kv_dtype == LP_BF16) LP_LAUNCH_ATT(float, __nv_bfloat16);

@@ -611,3 +611,191 @@ extern "C" int lp_advance(int* tokens, int* positions, int* kv_len, const int* s
     lp_launch(advance_kernel, (B + 127) / 128, 128, 0, stream, tokens, positions, kv_len, sampled, B);
     return lp_check_launch("advance");
 }
+
+// ---------------------------------------------------------------- queries, keys and values of a general attention layer
+// One block per token of the fused projection output
+//   qkv[t] = [ H query heads x dk | G key heads x dk | G value heads x dv ]   (float32),
+// for layers whose heads need more than a rotation: an additive bias per feature (`bias`, optional), the rotation of
+// the first `rd` features of every query and key head (pairs (2i, 2i+1) or (i, i + rd/2); angle = float(position) *
+// inv_freq[pair]; the pair (u, v) becomes (u cos - v sin, v cos + u sin)), and then (`unit`) the division of every
+// query and key head by its root mean square over dk, with `unit_eps` inside the root. Keys and values may differ in
+// size: queries, keys and values are stored with `hdp` features per head (hdp >= dk, dv), the rest zero, so that the
+// attention kernels see one head size; queries go to q_out[t, h, :hdp], keys and values to the page of the token's
+// sequence that holds its position, pages[page][0|1][g][position % page_size][:hdp]. A warp per head; all float32.
+constexpr int PREP_MAX = 256;
+template <typename TQ, typename TKV>
+__global__ void __launch_bounds__(256)
+qkv_prepare_kernel(const float* __restrict__ qkv, int ld, const float* __restrict__ bias, const float* __restrict__ inv_freq,
+                   const int* __restrict__ positions, const int* __restrict__ seq_ids, const int* __restrict__ page_table,
+                   int pt_stride, TQ* __restrict__ q_out, TKV* __restrict__ pages, int H, int G, int dk, int dv, int hdp,
+                   int rd, int interleaved, int unit, float unit_eps, int page_size) {
+    __shared__ float cs[PREP_MAX];
+    __shared__ float buf[8][PREP_MAX];
+    lp_grid_release();
+    lp_grid_wait();
+    const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int pos = positions[t];
+    const int half = rd >> 1;
+    for (int i = tid; i < half; i += blockDim.x) {
+        float s, c;
+        sincosf((float)pos * inv_freq[i], &s, &c);
+        cs[2 * i] = c;
+        cs[2 * i + 1] = s;
+    }
+    __syncthreads();
+    const float* row = qkv + (long long)t * ld;
+    const long long page = page_table[(long long)seq_ids[t] * pt_stride + pos / page_size];
+    const int r = pos % page_size;
+    for (int item = warp; item < H + 2 * G; item += 8) {
+        if (item < H + G) {
+            const int src = item * dk;               // query heads, then key heads, lie one after another
+            float ss = 0.f;
+            for (int e = lane; e < dk; e += 32) {
+                float val = row[src + e] + (bias ? bias[src + e] : 0.f);
+                if (e < rd) {
+                    int pair, partner;
+                    bool first;
+                    if (interleaved) { pair = e >> 1; first = !(e & 1); partner = e ^ 1; }
+                    else { first = e < half; pair = first ? e : e - half; partner = first ? e + half : e - half; }
+                    const float other = row[src + partner] + (bias ? bias[src + partner] : 0.f);
+                    const float c = cs[2 * pair], s = cs[2 * pair + 1];
+                    val = first ? val * c - other * s : val * c + other * s;
+                }
+                buf[warp][e] = val;
+                ss += val * val;
+            }
+            ss = lp_warp_sum(ss);
+            const float factor = unit ? 1.0f / sqrtf(ss / (float)dk + unit_eps) : 1.0f;
+            __syncwarp();
+            if (item < H) {
+                TQ* dst = q_out + ((long long)t * H + item) * hdp;
+                for (int e = lane; e < hdp; e += 32) dst[e] = lp_from_float<TQ>(e < dk ? buf[warp][e] * factor : 0.f);
+            } else {
+                TKV* dst = pages + (((page * 2 + 0) * G + (item - H)) * page_size + r) * hdp;
+                for (int e = lane; e < hdp; e += 32) dst[e] = lp_from_float<TKV>(e < dk ? buf[warp][e] * factor : 0.f);
+            }
+            __syncwarp();
+        } else {
+            const int g = item - H - G;
+            const int src = (H + G) * dk + g * dv;
+            TKV* dst = pages + (((page * 2 + 1) * G + g) * page_size + r) * hdp;
+            for (int e = lane; e < hdp; e += 32)
+                dst[e] = lp_from_float<TKV>(e < dv ? row[src + e] + (bias ? bias[src + e] : 0.f) : 0.f);
+        }
+    }
+}
+
+extern "C" int lp_qkv_prepare(const float* qkv, int ld, const float* bias, const float* inv_freq, const int* positions,
+                              const int* seq_ids, const int* page_table, int pt_stride, void* q_out, int q_dtype,
+                              void* pages, int kv_dtype, int T, int H, int G, int dk, int dv, int hdp, int rd,
+                              int interleaved, int unit, float unit_eps, int page_size, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || G <= 0 || dk <= 0 || dv <= 0) LP_REFUSE("qkv_prepare: %d / %d heads of %d and %d", H, G, dk, dv);
+    if (hdp < dk || hdp < dv || dk > PREP_MAX) LP_REFUSE("qkv_prepare: heads of %d and %d stored in %d (at most %d)", dk, dv, hdp, PREP_MAX);
+    if (rd < 0 || rd > dk || (rd & 1)) LP_REFUSE("qkv_prepare: rotary width %d for heads of %d", rd, dk);
+    if (rd > 0 && !inv_freq) LP_REFUSE("qkv_prepare: a rotation without frequencies");
+    if (ld < (H + G) * dk + G * dv) LP_REFUSE("qkv_prepare: rows of %d values for %d", ld, (H + G) * dk + G * dv);
+    if (page_size <= 0 || !pages) LP_REFUSE("qkv_prepare: needs the pages of the cache");
+#define LP_LAUNCH_PREP(TQ, TKV)                                                                                       \
+    lp_launch(qkv_prepare_kernel<TQ, TKV>, T, 256, 0, stream, qkv, ld, bias, inv_freq, positions, seq_ids, page_table, \
+              pt_stride, (TQ*)q_out, (TKV*)pages, H, G, dk, dv, hdp, rd, interleaved, unit, unit_eps, page_size)
+    if (q_dtype == LP_F32 && kv_dtype == LP_F32) LP_LAUNCH_PREP(float, float);
+    else if (q_dtype == LP_BF16 && kv_dtype == LP_BF16) LP_LAUNCH_PREP(__nv_bfloat16, __nv_bfloat16);
+    else LP_REFUSE("qkv_prepare: dtype codes q=%d kv=%d", q_dtype, kv_dtype);
+#undef LP_LAUNCH_PREP
+    return lp_check_launch("qkv_prepare");
+}
+
+// ---------------------------------------------------------------- norm of a sublayer's result, residual sum, next norm
+// x[t] += y[t] / sqrt(mean(y[t]^2) + eps) * w   (the norm that follows a sublayer, then the residual sum), and, when
+// `w2` is given, out2[t] = x[t] / sqrt(mean(x[t]^2) + eps2) * w2 (the norm in front of the next sublayer) in the same
+// pass. One block per row; float32; sums in a fixed order.
+template <typename TOut>
+__global__ void __launch_bounds__(NORM_THREADS)
+post_norm_add_kernel(const float* __restrict__ y, const float* __restrict__ w, float eps, float* __restrict__ x,
+                     const float* __restrict__ w2, float eps2, TOut* __restrict__ out2, int d) {
+    __shared__ float scratch[32];
+    lp_grid_release();
+    lp_grid_wait();
+    const long long row = blockIdx.x;
+    const float* yr = y + row * d;
+    float* xr = x + row * d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) ss += yr[i] * yr[i];
+    ss = lp_block_sum(ss, scratch);
+    const float f = 1.0f / sqrtf(ss / (float)d + eps);
+    float ss2 = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = xr[i] + yr[i] * f * w[i];
+        xr[i] = v;
+        ss2 += v * v;
+    }
+    if (!w2) return;
+    ss2 = lp_block_sum(ss2, scratch);
+    const float f2 = 1.0f / sqrtf(ss2 / (float)d + eps2);
+    TOut* o = out2 + row * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = lp_from_float<TOut>(xr[i] * f2 * w2[i]);
+}
+
+extern "C" int lp_post_norm_add(const float* y, const float* w, float eps, float* x, const float* w2, float eps2,
+                                void* out2, int out2_dtype, int T, int d, cudaStream_t stream) {
+    if (T <= 0 || d <= 0) return 0;
+    if (w2 && !out2) LP_REFUSE("post_norm_add: a second norm without its output");
+    if (!w2 || out2_dtype == LP_F32)
+        lp_launch(post_norm_add_kernel<float>, T, NORM_THREADS, 0, stream, y, w, eps, x, w2, eps2, (float*)out2, d);
+    else if (out2_dtype == LP_BF16)
+        lp_launch(post_norm_add_kernel<__nv_bfloat16>, T, NORM_THREADS, 0, stream, y, w, eps, x, w2, eps2, (__nv_bfloat16*)out2, d);
+    else LP_REFUSE("post_norm_add: output dtype code %d", out2_dtype);
+    return lp_check_launch("post_norm_add");
+}
+
+// ---------------------------------------------------------------- additions to the stream between runs of layers
+// x[t, i] += other[t, i] + vec[i]; either may be absent. float32.
+__global__ void __launch_bounds__(256)
+stream_add_kernel(float* __restrict__ x, const float* __restrict__ other, const float* __restrict__ vec, int T, int d) {
+    lp_grid_release();
+    lp_grid_wait();
+    const long long n = (long long)T * d;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        float v = x[i];
+        if (other) v += other[i];
+        if (vec) v += vec[i % d];
+        x[i] = v;
+    }
+}
+
+extern "C" int lp_stream_add(float* x, const float* other, const float* vec, int T, int d, cudaStream_t stream) {
+    if (T <= 0 || d <= 0 || (!other && !vec)) return 0;
+    const long long n = (long long)T * d;
+    long long blocks = (n + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    lp_launch(stream_add_kernel, (unsigned)blocks, 256, 0, stream, x, other, vec, T, d);
+    return lp_check_launch("stream_add");
+}
+
+// ---------------------------------------------------------------- squared ReLU
+// out[t, f] = max(z[t, f], 0)^2 on the float32 sums of an up projection (z: [T, ldz], may be a slice).
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+relu2_kernel(const float* __restrict__ z, int ldz, TOut* __restrict__ out, int T, int F) {
+    lp_grid_release();
+    lp_grid_wait();
+    const long long n = (long long)T * F;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / F;
+        const float v = fmaxf(z[t * ldz + (i - t * F)], 0.f);
+        out[i] = lp_from_float<TOut>(v * v);
+    }
+}
+
+extern "C" int lp_relu2(const float* z, int ldz, void* out, int out_dtype, int T, int F, cudaStream_t stream) {
+    if (T <= 0 || F <= 0) return 0;
+    if (ldz < F) LP_REFUSE("relu2: rows of %d values for %d features", ldz, F);
+    const long long n = (long long)T * F;
+    long long blocks = (n + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (out_dtype == LP_F32) lp_launch(relu2_kernel<float>, (unsigned)blocks, 256, 0, stream, z, ldz, (float*)out, T, F);
+    else if (out_dtype == LP_BF16) lp_launch(relu2_kernel<__nv_bfloat16>, (unsigned)blocks, 256, 0, stream, z, ldz, (__nv_bfloat16*)out, T, F);
+    else LP_REFUSE("relu2: output dtype code %d", out_dtype);
+    return lp_check_launch("relu2");
+}

@@ -54,6 +54,10 @@ constexpr int TB = 16;            // tokens per round of loads
 //   chunk's start state where its local state was, and the last one into the sequence's state row)
 //   mode OUTPUT   every chunk starts from its start state and writes its outputs.
 // mode WHOLE is the recurrence in one pass, from and into the sequence's state row (decode steps, short prompts).
+// Variants that other recurrences of this family need: `decay_per_head` (one decay per token and head, decay [T, H], for
+// all its key channels), `key_gain` [T, H] (the key of a token is multiplied by it: an input gate), and `ones` (the last of
+// the dv value columns is the constant 1 and the projection holds dv - 1 columns per head: that column of the state is
+// then the decayed sum of the gated keys, and its output their product with the query: a normaliser).
 constexpr int SCAN_WHOLE = 0, SCAN_LOCAL = 1, SCAN_OUTPUT = 2;
 
 template <int KP, int VT, int KPT, int JT>
@@ -61,7 +65,8 @@ __global__ void __launch_bounds__(VT / JT * KP)
 gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off, const float* __restrict__ decay,
                 float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ q_start,
                 float* __restrict__ out, int H, int dk, int dv, float q_scale, int mode, int chunks, int chunk,
-                float* __restrict__ chunk_state, float* __restrict__ chunk_decay) {
+                float* __restrict__ chunk_state, float* __restrict__ chunk_decay, int decay_per_head,
+                const float* __restrict__ key_gain, int ones) {
     extern __shared__ float sm[];
     float* qs = sm;                         // [TB][dk]
     float* ks = qs + TB * dk;
@@ -98,13 +103,14 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
             const int i = e / dk, c = e - i * dk;
             const float* row = proj + (long long)(tb + i) * ld;
             qs[e] = row[q_off + h * dk + c] * q_scale;
-            ks[e] = row[k_off + h * dk + c];
-            as[e] = decay[((long long)(tb + i) * H + h) * dk + c];
+            ks[e] = row[k_off + h * dk + c] * (key_gain ? key_gain[(long long)(tb + i) * H + h] : 1.0f);
+            as[e] = decay_per_head ? decay[(long long)(tb + i) * H + h] : decay[((long long)(tb + i) * H + h) * dk + c];
         }
         for (int e = tid; e < nt * VT; e += blockDim.x) {
             const int i = e / VT, c = e - i * VT;
             const int col = blockIdx.x * VT + c;
-            vs[e] = col < dv ? proj[(long long)(tb + i) * ld + v_off + h * dv + col] : 0.f;
+            const int dvin = dv - ones;             // value columns that come from the projection
+            vs[e] = col < dvin ? proj[(long long)(tb + i) * ld + v_off + h * dvin + col] : (col < dv ? 1.0f : 0.f);
         }
         __syncthreads();
         for (int i = 0; i < nt; ++i) {
@@ -180,12 +186,62 @@ gla_combine_kernel(float* __restrict__ state, const int* __restrict__ slots, con
     *row = s;
 }
 
+// ---------------------------------------------------------------- exponential gates with a running maximum
+// Per token and head, from the pre-activations zi, zf (float32 columns of the projection) and their biases:
+//     i = cap * tanh((zi + bi) / cap)                       the logarithm of the input gate
+//     f = logsigmoid(cap * tanh((zf + bf) / cap))           the logarithm of the forget gate
+//     m_t = max(f + m_(t-1), i)                             the running maximum (the sequence's m starts at 0)
+//     decay[t] = exp(f + m_(t-1) - m_t),  gain[t] = exp(i - m_t),  max_row[t] = m_t
+// so that S_t = decay S_(t-1) + gain k v^T is the recurrence in a stabilised form (matrix memory of the xLSTM family).
+// One block per sequence: all threads form i and f of its new tokens, then one thread per head walks them in order.
+// m is kept per slot and head in `mstate`.
+__device__ __forceinline__ float lp_log_sigmoid(float v) { return -(fmaxf(-v, 0.f) + log1pf(expf(-fabsf(v)))); }
+
+__global__ void __launch_bounds__(256)
+exp_gates_kernel(const float* __restrict__ proj, int ld, int i_off, int f_off, const float* __restrict__ bias_i,
+                 const float* __restrict__ bias_f, float cap, float* __restrict__ mstate, const int* __restrict__ slots,
+                 const int* __restrict__ q_start, float* __restrict__ decay, float* __restrict__ gain,
+                 float* __restrict__ max_row, int H) {
+    lp_grid_release();
+    lp_grid_wait();
+    const int b = blockIdx.x;
+    const int t0 = q_start[b], t1 = q_start[b + 1];
+    const int n = (t1 - t0) * H;
+    for (int e = threadIdx.x; e < n; e += blockDim.x) {
+        const int t = t0 + e / H, h = e % H;
+        const float zi = proj[(long long)t * ld + i_off + h] + (bias_i ? bias_i[h] : 0.f);
+        const float zf = proj[(long long)t * ld + f_off + h] + (bias_f ? bias_f[h] : 0.f);
+        const float li = cap > 0.f ? cap * tanhf(zi / cap) : zi;
+        const float lf = lp_log_sigmoid(cap > 0.f ? cap * tanhf(zf / cap) : zf);
+        gain[(long long)t * H + h] = li;
+        decay[(long long)t * H + h] = lf;
+    }
+    __syncthreads();
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        float* ms = mstate + (long long)slots[b] * H + h;
+        float m = *ms;
+        for (int t = t0; t < t1; ++t) {
+            const long long at = (long long)t * H + h;
+            const float li = gain[at], lf = decay[at];
+            const float mn = fmaxf(lf + m, li);
+            decay[at] = expf(lf + m - mn);
+            gain[at] = expf(li - mn);
+            max_row[at] = mn;
+            m = mn;
+        }
+        *ms = m;
+    }
+}
+
 // ---------------------------------------------------------------- finish
 // out[t, h * dv + j] = o[t, h, j] / sqrt(mean_j o^2 + eps) * gain[j] * silu(gate[t, h * dv + j]); a warp per (t, h).
+// Variants: rows of o that are `xs` apart (xs > dv: further columns follow a head's values), a gain per head
+// (`gain_per_head`: gain [H * dv]), a sigmoid instead of the silu (`gate_sigmoid`), and `max_row` [T, H] (see the kernel).
 template <typename TOut>
 __global__ void __launch_bounds__(256)
 gla_finish_kernel(const float* __restrict__ o, const float* __restrict__ gain, float eps, const float* __restrict__ gate,
-                  int ldg, TOut* __restrict__ out, int T, int H, int dv, float* __restrict__ zero, long long zero_count) {
+                  int ldg, TOut* __restrict__ out, int T, int H, int dv, float* __restrict__ zero, long long zero_count,
+                  int xs, int gain_per_head, int gate_sigmoid, const float* __restrict__ max_row) {
     lp_grid_release();
     lp_grid_wait();
     clear_on_the_side(zero, zero_count);
@@ -194,15 +250,21 @@ gla_finish_kernel(const float* __restrict__ o, const float* __restrict__ gain, f
     if (row >= (long long)T * H) return;
     const long long t = row / H;
     const int h = (int)(row - t * H);
-    const float* x = o + row * dv;
+    const float* x = o + row * xs;
+    // with a normaliser column (x[dv]) and the row's running maximum m: x / (max(|x[dv]|, exp(-m)) + 1e-6) first
+    const float pre = max_row ? 1.0f / (fmaxf(fabsf(x[dv]), expf(-max_row[row])) + 1e-6f) : 1.0f;
     float ss = 0.f;
-    for (int j = lane; j < dv; j += 32) ss += x[j] * x[j];
-    ss = lp_warp_sum(ss);
-    const float factor = 1.0f / sqrtf(ss / (float)dv + eps);
-    const float* g = gate ? gate + t * ldg + (long long)h * dv : nullptr;
     for (int j = lane; j < dv; j += 32) {
-        float v = x[j] * factor * gain[j];
-        if (g) v *= g[j] / (1.0f + expf(-g[j]));
+        const float v = x[j] * pre;
+        ss += v * v;
+    }
+    ss = lp_warp_sum(ss);
+    const float factor = pre / sqrtf(ss / (float)dv + eps);
+    const float* g = gate ? gate + t * ldg + (long long)h * dv : nullptr;
+    const float* gn = gain_per_head ? gain + (long long)h * dv : gain;
+    for (int j = lane; j < dv; j += 32) {
+        float v = x[j] * factor * gn[j];
+        if (g) v *= gate_sigmoid ? 1.0f / (1.0f + expf(-g[j])) : g[j] / (1.0f + expf(-g[j]));
         out[row * dv + j] = lp_from_float<TOut>(v);
     }
 }
@@ -232,14 +294,16 @@ extern "C" int lp_gla_decay(const float* low, int ldl, const void* a2, int w_dty
 extern "C" int lp_gla_scan(const float* proj, int ld, int q_off, int k_off, int v_off, const float* decay, float* state,
                            const int* slots, const int* q_start, float* out, int B, int H, int dk, int dv,
                            float q_scale, int chunks, int chunk, float* chunk_state, float* chunk_decay,
-                           cudaStream_t stream) {
+                           int decay_per_head, const float* key_gain, int ones, cudaStream_t stream) {
     if (B <= 0) return 0;
     if (chunks < 1) chunks = 1;
+    ones = ones ? 1 : 0;
+    if (dv - ones <= 0) LP_REFUSE("gla_scan: %d value columns, %d of them constant", dv, ones);
     if (chunks > 1 && (chunk <= 0 || !chunk_state || !chunk_decay)) LP_REFUSE("gla_scan: %d chunks without their buffers", chunks);
     if ((long long)B * chunks > 65535) LP_REFUSE("gla_scan: %d sequences in %d chunks exceed the grid", B, chunks);
     if (H <= 0 || H > 65535 || B > 65535 || dk <= 0 || dv <= 0) LP_REFUSE("gla_scan: %d sequences, %d heads of %d x %d", B, H, dk, dv);
     if (dk > 512) LP_REFUSE("gla_scan: %d key channels per head (supported: up to 512)", dk);
-    if (q_off < 0 || k_off < 0 || v_off < 0 || q_off + H * dk > ld || k_off + H * dk > ld || v_off + H * dv > ld)
+    if (q_off < 0 || k_off < 0 || v_off < 0 || q_off + H * dk > ld || k_off + H * dk > ld || v_off + H * (dv - (ones ? 1 : 0)) > ld)
         LP_REFUSE("gla_scan: slices at %d, %d, %d do not fit rows of %d", q_off, k_off, v_off, ld);
 #define LP_LAUNCH_SCAN(KP_, VT_, N, JT_)                                                                                 \
     do {                                                                                                              \
@@ -252,17 +316,17 @@ extern "C" int lp_gla_scan(const float* proj, int ld, int q_off, int k_off, int 
         if (chunks == 1) {                                                                                            \
             lp_launch(gla_scan_kernel<KP_, VT_, N, JT_>, grid, VT_ / JT_ * KP_, smem, stream, proj, ld, q_off, k_off, v_off,     \
                       decay, state, slots, q_start, out, H, dk, dv, q_scale, SCAN_WHOLE, 1, 0, (float*)nullptr,       \
-                      (float*)nullptr);                                                                               \
+                      (float*)nullptr, decay_per_head, key_gain, ones);                                                                               \
         } else {                                                                                                      \
             lp_launch(gla_scan_kernel<KP_, VT_, N, JT_>, grid, VT_ / JT_ * KP_, smem, stream, proj, ld, q_off, k_off, v_off,     \
                       decay, state, slots, q_start, out, H, dk, dv, q_scale, SCAN_LOCAL, chunks, chunk, chunk_state,  \
-                      chunk_decay);                                                                                   \
+                      chunk_decay, decay_per_head, key_gain, ones);                                                                                   \
             const long long per = (long long)H * dv * dk;                                                             \
             lp_launch(gla_combine_kernel, dim3((unsigned)((per + 255) / 256), B), 256, 0, stream, state, slots,       \
                       q_start, chunk_state, (const float*)chunk_decay, H, dk, dv, chunks, chunk);                     \
             lp_launch(gla_scan_kernel<KP_, VT_, N, JT_>, grid, VT_ / JT_ * KP_, smem, stream, proj, ld, q_off, k_off, v_off,     \
                       decay, state, slots, q_start, out, H, dk, dv, q_scale, SCAN_OUTPUT, chunks, chunk, chunk_state, \
-                      chunk_decay);                                                                                   \
+                      chunk_decay, decay_per_head, key_gain, ones);                                                                                   \
         }                                                                                                             \
     } while (0)
     // few key channels: 4 threads per column, 64 columns per CTA; from 32 channels on: 16 threads per column, 16 columns
@@ -279,14 +343,30 @@ extern "C" int lp_gla_scan(const float* proj, int ld, int q_off, int k_off, int 
 }
 
 extern "C" int lp_gla_finish(const float* o, const float* gain, float eps, const float* gate, int ldg, void* out,
-                             int out_dtype, int T, int H, int dv, float* zero, long long zero_count, cudaStream_t stream) {
+                             int out_dtype, int T, int H, int dv, float* zero, long long zero_count, int xs,
+                             int gain_per_head, int gate_sigmoid, const float* max_row, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || dv <= 0) LP_REFUSE("gla_finish: %d heads of %d", H, dv);
+    if (xs <= 0) xs = dv;
+    if (xs < dv || (max_row && xs < dv + 1)) LP_REFUSE("gla_finish: rows %d apart for %d values", xs, dv);
     const long long rows = (long long)T * H;
     const unsigned blocks = (unsigned)((rows + 7) / 8);
-    if (out_dtype == LP_F32) lp_launch(gla_finish_kernel<float>, blocks, 256, 0, stream, o, gain, eps, gate, ldg, (float*)out, T, H, dv, zero, zero_count);
+    if (out_dtype == LP_F32) lp_launch(gla_finish_kernel<float>, blocks, 256, 0, stream, o, gain, eps, gate, ldg, (float*)out, T, H, dv, zero, zero_count, xs, gain_per_head, gate_sigmoid, max_row);
     else if (out_dtype == LP_BF16)
-        lp_launch(gla_finish_kernel<__nv_bfloat16>, blocks, 256, 0, stream, o, gain, eps, gate, ldg, (__nv_bfloat16*)out, T, H, dv, zero, zero_count);
+        lp_launch(gla_finish_kernel<__nv_bfloat16>, blocks, 256, 0, stream, o, gain, eps, gate, ldg, (__nv_bfloat16*)out, T, H, dv, zero, zero_count, xs, gain_per_head, gate_sigmoid, max_row);
     else LP_REFUSE("gla_finish: output dtype code %d", out_dtype);
     return lp_check_launch("gla_finish");
+}
+
+// proj: float32 [T, ld] with the input gate's pre-activations at i_off and the forget gate's at f_off (H each);
+// bias_i, bias_f: float32 [H] or null; cap <= 0: no cap. mstate: float32 [slots, H]; decay, gain, max_row: float32 [T, H].
+extern "C" int lp_exp_gates(const float* proj, int ld, int i_off, int f_off, const float* bias_i, const float* bias_f,
+                            float cap, float* mstate, const int* slots, const int* q_start, float* decay, float* gain,
+                            float* max_row, int B, int H, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (H <= 0 || i_off < 0 || f_off < 0 || i_off + H > ld || f_off + H > ld)
+        LP_REFUSE("exp_gates: %d heads at %d and %d in rows of %d", H, i_off, f_off, ld);
+    lp_launch(exp_gates_kernel, B, 256, 0, stream, proj, ld, i_off, f_off, bias_i, bias_f, cap, mstate, slots, q_start,
+              decay, gain, max_row, H);
+    return lp_check_launch("exp_gates");
 }

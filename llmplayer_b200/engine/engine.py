@@ -55,7 +55,7 @@ class Engine:
         self._prepared = None          # (context, page tables): the next decode step's pages, reserved ahead
         from ..cache.sequence_cache import StateRequest
         # whether a run keeps a state that a step changes in place (running a step twice would change it twice)
-        self._keeps_state = any(isinstance(r, StateRequest) for r in model.cache_requests())
+        self._keeps_state = any(isinstance(r, StateRequest) or (isinstance(r, tuple) and r) for r in model.cache_requests())
 
     # ------------------------------------------------------------------ construction
     @classmethod

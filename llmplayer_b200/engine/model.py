@@ -16,7 +16,8 @@ from ..errors import ConfigError
 from ..parts import BLOCKS
 from ..parts.base import Runtime
 from ..parts.embedding import Embedding, LinearHead
-from ..parts.specs import ModelLayout, TensorSpec
+from ..kernels import ops
+from ..parts.specs import BIAS, ModelLayout, TensorSpec
 
 
 class Model:
@@ -32,6 +33,15 @@ class Model:
             if run.reads_cache_of is not None and not 0 <= run.reads_cache_of < i:
                 raise ConfigError(f"run {i} reads the cache of run {run.reads_cache_of}, which does not precede it")
         self.runtime: Optional[Runtime] = None
+        # what some runs add to the stream before they start: the embedding's output, a row of a learned table
+        self._keeps_embedding = any(run.add_embedding for run in self.runs)
+        self._vector_rows: Dict[str, int] = {}
+        for run in self.runs:
+            if run.add_vector is not None:
+                if run.add_row < 0:
+                    raise ConfigError(f"row {run.add_row} of {run.add_vector!r}")
+                self._vector_rows[run.add_vector] = max(self._vector_rows.get(run.add_vector, 0), run.add_row + 1)
+        self._vectors: Dict[str, torch.Tensor] = {}
         # blocks whose forward takes (normed_ready, next_block) can hand a fused norm to the next block
         self._chains = ["next_block" in inspect.signature(b.forward).parameters for b in self.blocks]
 
@@ -51,6 +61,8 @@ class Model:
                 if name in out and out[name] != spec:
                     raise ConfigError(f"tensor {name!r} is asked for with shapes {out[name].shape} and {spec.shape}")
                 out[name] = spec
+        for name, rows in self._vector_rows.items():
+            out[name] = TensorSpec((rows, self.layout.embedding.hidden_size), BIAS)
         return out
 
     def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
@@ -59,6 +71,7 @@ class Model:
         for block in self.blocks:
             block.load(tensors, runtime)
         self.head.load(tensors, runtime)
+        self._vectors = {name: runtime.gain(tensors[name]) for name in self._vector_rows}
         runtime.forget_uploads()
 
     # ------------------------------------------------------------------ cache
@@ -77,9 +90,18 @@ class Model:
         d = self.layout.embedding.hidden_size
         x = ctx.buffer("residual", (ctx.num_tokens, d), torch.float32)
         self.embedding.forward(ctx.tokens, x)
+        x0 = None
+        if self._keeps_embedding:
+            x0 = ctx.buffer("embedding_out", (ctx.num_tokens, d), torch.float32)
+            x0.copy_(x)
         ready = False        # whether the previous block already normed the stream for this one
         for i, run in enumerate(self.runs):
             block = self.blocks[run.layer]
+            if run.add_embedding or run.add_vector is not None:
+                with ops.section("stream.add"):
+                    ops.stream_add(x, x0 if run.add_embedding else None,
+                                   self._vectors[run.add_vector][run.add_row] if run.add_vector is not None else None)
+                ready = False
             following = self.blocks[self.runs[i + 1].layer] if i + 1 < len(self.runs) else None
             if self._chains[run.layer]:
                 ready = bool(block.forward(ctx, cache.view(self.cache_owner(i)), x, normed_ready=ready,

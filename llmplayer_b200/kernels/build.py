@@ -36,6 +36,7 @@ LIBRARIES: Dict[str, str] = {
     "host_loop": "host_loop.cu",
     "latent_attention": "latent_attention.cu",
     "linear_attention": "linear_attention.cu",
+    "routing": "routing.cu",
 }
 HEADERS = ("common.cuh", "attention_noalloc.h", "tcgen05_utils.cuh", "attention_decode.cuh")
 

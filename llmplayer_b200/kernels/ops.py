@@ -31,12 +31,20 @@ _SIGNATURES = {
         "lp_rope_cache_write": [_P, _I, _P, _P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
         "lp_advance": [_P, _P, _P, _P, _I, _P],
         "lp_rope_angles": [_P, _P, _P, _I, _I, _P],
+        "lp_qkv_prepare": [_P, _I, _P, _P, _P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+        "lp_post_norm_add": [_P, _P, _F, _P, _P, _F, _P, _I, _I, _I, _P],
+        "lp_stream_add": [_P, _P, _P, _I, _I, _P],
+        "lp_relu2": [_P, _I, _P, _I, _I, _I, _P],
+    },
+    "routing": {
+        "lp_route": [_P, _I, _P, _I, _I, _I, _I, _I, _I, _P],
+        "lp_expert_scale": [_P, _I, _I, _P, _I, _I, _I, _I, _P],
     },
     "gemm_plain": {
         "lp_gemm_plain": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     },
     "attention_plain": {
-        "lp_attention_plain": [_P, _P, _I, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
+        "lp_attention_plain": [_P, _P, _I, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _F, _P, _P],
     },
     "gemm_tcgen05": {
         "lp_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P,
@@ -47,9 +55,9 @@ _SIGNATURES = {
         "lp_gemm_qkv_rope": [_P, _P, _I, _I, _I, _I, _P, _I, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _P, _P],
     },
     "attention_mma": {
-        "lp_attention_prefill": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
-        "lp_attention_decode": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
-        "lp_attention_decode_fitted": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
+        "lp_attention_prefill": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _F, _P, _P],
+        "lp_attention_decode": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _P],
+        "lp_attention_decode_fitted": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _P],
         "lp_attention_decode_fused": [_P, _I, _P, _I, _I, _P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I,
                                       _I, _I, _I, _P, _F, _I, ctypes.c_longlong, _P, _P],
     },
@@ -70,8 +78,9 @@ _SIGNATURES = {
     },
     "linear_attention": {
         "lp_gla_decay": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _F, _P],
-        "lp_gla_scan": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _P],
-        "lp_gla_finish": [_P, _P, _F, _P, _I, _P, _I, _I, _I, _I, _P, ctypes.c_longlong, _P],
+        "lp_gla_scan": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, _P, _I, _P],
+        "lp_gla_finish": [_P, _P, _F, _P, _I, _P, _I, _I, _I, _I, _P, ctypes.c_longlong, _I, _I, _I, _P, _P],
+        "lp_exp_gates": [_P, _I, _I, _I, _P, _P, _F, _P, _P, _P, _P, _P, _P, _I, _I, _P],
     },
     "host_loop": {
         "lp_decode_loop": [_P, _P, _P, _I, _I, _I, _P, _I, _I, _P, _P, _P, _P, _P],
@@ -821,9 +830,12 @@ def gemm_few(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = ST
 # --------------------------------------------------------------------------- attention
 def attention_plain(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, page_table: torch.Tensor,
                     seq_ids: torch.Tensor, positions: torch.Tensor, *, num_heads: int, num_kv_heads: int,
-                    head_dim: int, scale: float, window: Optional[int]) -> torch.Tensor:
+                    head_dim: int, scale: float, window: Optional[int], softcap: Optional[float] = None,
+                    sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Each query token attends over the cached keys of its sequence up to its own
-    position (and within ``window``, if given)."""
+    position (and within ``window``, if given). ``softcap``: scores become softcap * tanh(score / softcap) after the
+    scale; ``sinks``: float32 [H], a logit per head that enters the softmax's denominator once."""
+    _check_sinks(sinks, num_heads, "attention")
     _want(q, "attention q", ndim=2)
     _want(out, "attention out", q.dtype, 2)
     _want(pages, "attention pages", ndim=5)
@@ -840,8 +852,15 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, pag
     _check(lib, lib.lp_attention_plain(
         q.data_ptr(), out.data_ptr(), _code(q, "attention q"), pages.data_ptr(), _code(pages, "attention pages"),
         page_table.data_ptr(), page_table.shape[1], seq_ids.data_ptr(), positions.data_ptr(), T, H, G, hd,
-        pages.shape[3], float(scale), int(window) if window else 0, _stream()))
+        pages.shape[3], float(scale), int(window) if window else 0, float(softcap or 0.0), _ptr(sinks), _stream()))
     return out
+
+
+def _check_sinks(sinks: Optional[torch.Tensor], num_heads: int, what: str) -> None:
+    if sinks is not None:
+        _want(sinks, f"{what} sinks", torch.float32, 1)
+        if sinks.numel() != num_heads:
+            raise KernelError(f"{what}: {sinks.numel()} sinks for {num_heads} heads")
 
 
 def _check_attention(q, out, pages, page_table, H, G, hd, what):
@@ -860,7 +879,8 @@ tcgen05_attention = True      # tests switch it off to reach the mma.sync kernel
 
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, page_table: torch.Tensor,
                       q_start: torch.Tensor, kv_len: torch.Tensor, max_new: int, *, num_heads: int,
-                      num_kv_heads: int, head_dim: int, scale: float, window: Optional[int]) -> torch.Tensor:
+                      num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
+                      softcap: Optional[float] = None, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Tensor-core attention for a step that brings several tokens per sequence.
     ``q_start`` [B+1]: offsets of each sequence's new tokens; ``kv_len`` [B]: lengths after the step."""
     _check_attention(q, out, pages, page_table, num_heads, num_kv_heads, head_dim, "attention_prefill")
@@ -869,7 +889,8 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, p
     B = kv_len.numel()
     if q_start.numel() != B + 1 or page_table.shape[0] != B:
         raise KernelError(f"attention_prefill: {B} sequences, {q_start.numel()} offsets, table {tuple(page_table.shape)}")
-    if head_dim in (64, 128) and max_new > 64 and tcgen05_attention:
+    _check_sinks(sinks, num_heads, "attention_prefill")
+    if head_dim in (64, 128) and max_new > 64 and tcgen05_attention and not softcap and sinks is None:
         # long runs of new tokens with heads of 64 or 128: scores and P V on the tcgen05 tensor cores
         lib = library("attention_tcgen05")
         _check(lib, lib.lp_attention_prefill_tc(
@@ -882,7 +903,7 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, p
     _check(lib, lib.lp_attention_prefill(
         q.data_ptr(), out.data_ptr(), pages.data_ptr(), page_table.data_ptr(), page_table.shape[1],
         q_start.data_ptr(), kv_len.data_ptr(), B, int(max_new), num_heads, num_kv_heads, head_dim, pages.shape[3],
-        float(scale), int(window) if window else 0, _stream()))
+        float(scale), int(window) if window else 0, float(softcap or 0.0), _ptr(sinks), _stream()))
     return out
 
 
@@ -910,11 +931,13 @@ def decode_split(batch: int, num_kv_heads: int, num_heads: int, table_width: int
 
 def attention_decode(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, page_table: torch.Tensor,
                      kv_len: torch.Tensor, scratch, *, num_heads: int, num_kv_heads: int, head_dim: int,
-                     scale: float, window: Optional[int], pages_per_split: int = 0, num_splits: int = 0) -> torch.Tensor:
+                     scale: float, window: Optional[int], pages_per_split: int = 0, num_splits: int = 0,
+                     softcap: Optional[float] = None, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Tensor-core attention for a step of one token per sequence. ``scratch(name, shape, dtype)``
     supplies the float32 buffer for the partial results of the shares."""
     _check_attention(q, out, pages, page_table, num_heads, num_kv_heads, head_dim, "attention_decode")
     _want(kv_len, "attention_decode kv_len", torch.int32, 1)
+    _check_sinks(sinks, num_heads, "attention_decode")
     B = kv_len.numel()
     if q.shape[0] != B or page_table.shape[0] != B:
         raise KernelError(f"attention_decode: {B} sequences, q {tuple(q.shape)}, table {tuple(page_table.shape)}")
@@ -927,12 +950,12 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, pa
         _check(lib, lib.lp_attention_decode_fitted(
             q.data_ptr(), out.data_ptr(), pages.data_ptr(), page_table.data_ptr(), page_table.shape[1],
             kv_len.data_ptr(), buf.data_ptr(), B, num_heads, num_kv_heads, head_dim, pages.shape[3], float(scale),
-            int(window) if window else 0, num_splits, MIN_SHARE_PAGES, _stream()))
+            int(window) if window else 0, num_splits, MIN_SHARE_PAGES, float(softcap or 0.0), _ptr(sinks), _stream()))
         return out
     _check(lib, lib.lp_attention_decode(
         q.data_ptr(), out.data_ptr(), pages.data_ptr(), page_table.data_ptr(), page_table.shape[1], kv_len.data_ptr(),
         buf.data_ptr(), B, num_heads, num_kv_heads, head_dim, pages.shape[3], float(scale),
-        int(window) if window else 0, pages_per_split, num_splits, _stream()))
+        int(window) if window else 0, pages_per_split, num_splits, float(softcap or 0.0), _ptr(sinks), _stream()))
     return out
 
 
@@ -993,19 +1016,21 @@ def attention_decode_fused(qkv: torch.Tensor, rotation: Rotation, out: torch.Ten
 
 def attention(ctx, q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, page_table: torch.Tensor, *,
               num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
-              fast: bool) -> torch.Tensor:
+              fast: bool, softcap: Optional[float] = None, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of the step's tokens over the cache; picks the kernel for the step's shape."""
     tensor_cores = (fast and q.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16
                     and head_dim % 16 == 0 and head_dim <= 256)
     if tensor_cores and ctx.all_single:
         return attention_decode(q, out, pages, page_table, ctx.kv_len, ctx.buffer, num_heads=num_heads,
-                                num_kv_heads=num_kv_heads, head_dim=head_dim, scale=scale, window=window)
+                                num_kv_heads=num_kv_heads, head_dim=head_dim, scale=scale, window=window,
+                                softcap=softcap, sinks=sinks)
     if tensor_cores:
         return attention_prefill(q, out, pages, page_table, ctx.q_start, ctx.kv_len, ctx.max_new,
                                  num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim, scale=scale,
-                                 window=window)
+                                 window=window, softcap=softcap, sinks=sinks)
     return attention_plain(q, out, pages, page_table, ctx.seq_ids, ctx.positions, num_heads=num_heads,
-                           num_kv_heads=num_kv_heads, head_dim=head_dim, scale=scale, window=window)
+                           num_kv_heads=num_kv_heads, head_dim=head_dim, scale=scale, window=window, softcap=softcap,
+                           sinks=sinks)
 
 
 # --------------------------------------------------------------------------- latent attention
@@ -1215,14 +1240,20 @@ GLA_CHUNKED_FROM = 256        # from how many new tokens of a sequence on the ch
 
 def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torch.Tensor, state: torch.Tensor,
              slots: torch.Tensor, q_start: torch.Tensor, out: torch.Tensor, *, num_heads: int, key_dim: int,
-             value_dim: int, q_scale: float, max_new: int = 0, scratch=None) -> torch.Tensor:
+             value_dim: int, q_scale: float, max_new: int = 0, scratch=None, decay_per_head: bool = False,
+             key_gain: Optional[torch.Tensor] = None, ones_column: bool = False) -> torch.Tensor:
     """The recurrence S <- diag(decay_t) S + k_t v_t^T, out_t = S^T (q_t * q_scale) over the step's tokens of every
     sequence, from and into ``state`` float32 [slots, H, dv, dk] (row ``slots[b]`` for sequence b; a value column's
     key channels lie together). ``proj``: float32
     [T, F] with queries, keys and values at the given columns; ``decay``: float32 [T, H * dk]; ``out``: float32 [T, H * dv].
     With ``max_new`` (the most new tokens of a sequence) of ``GLA_CHUNKED_FROM`` or more and ``scratch(name, shape,
     dtype)`` for buffers, the sequences are cut into chunks of ``GLA_CHUNK`` tokens that run side by side: each
-    chunk's own contribution from a zero state, then the chunks' start states in order, then the outputs."""
+    chunk's own contribution from a zero state, then the chunks' start states in order, then the outputs.
+
+    ``decay_per_head``: ``decay`` is float32 [T, H], one decay per token and head for all its key channels.
+    ``key_gain``: float32 [T, H], multiplied into the token's keys (an input gate). ``ones_column``: the last of the
+    ``value_dim`` columns of state and output is fed the constant 1 instead of a value (the projection then holds
+    ``value_dim - 1`` values per head): its output is q . (decayed sum of the gated keys), a normaliser."""
     _want(proj, "gla_scan proj", torch.float32, 2)
     _want(decay, "gla_scan decay", torch.float32, 2)
     _want(state, "gla_scan state", torch.float32, 4)
@@ -1232,7 +1263,11 @@ def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torc
     T = proj.shape[0]
     H, dk, dv = num_heads, key_dim, value_dim
     B = slots.numel()
-    if (decay.shape != (T, H * dk) or state.shape[1:] != (H, dv, dk) or out.shape != (T, H * dv)
+    if key_gain is not None:
+        _want(key_gain, "gla_scan key_gain", torch.float32, 2)
+        if key_gain.shape != (T, H):
+            raise KernelError(f"gla_scan: key gains {tuple(key_gain.shape)} for {T} tokens and {H} heads")
+    if (decay.shape != (T, H if decay_per_head else H * dk) or state.shape[1:] != (H, dv, dk) or out.shape != (T, H * dv)
             or q_start.numel() != B + 1):
         raise KernelError(f"gla_scan: proj {tuple(proj.shape)}, decay {tuple(decay.shape)}, state {tuple(state.shape)}, "
                           f"out {tuple(out.shape)}, {B} sequences")
@@ -1244,32 +1279,186 @@ def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torc
     lib = library("linear_attention")
     _check(lib, lib.lp_gla_scan(proj.data_ptr(), proj.shape[1], int(q_off), int(k_off), int(v_off), decay.data_ptr(),
                                 state.data_ptr(), slots.data_ptr(), q_start.data_ptr(), out.data_ptr(), B, H, dk, dv,
-                                float(q_scale), chunks, GLA_CHUNK, _ptr(chunk_state), _ptr(chunk_decay), _stream()))
+                                float(q_scale), chunks, GLA_CHUNK, _ptr(chunk_state), _ptr(chunk_decay),
+                                1 if decay_per_head else 0, _ptr(key_gain), 1 if ones_column else 0, _stream()))
     if chunks > 1:
         count_launches(2)
     return out
 
 
 def gla_finish(o: torch.Tensor, gain: torch.Tensor, eps: float, gate: Optional[torch.Tensor], out: torch.Tensor, *,
-               num_heads: int, value_dim: int, clear: Optional[torch.Tensor] = None) -> torch.Tensor:
+               num_heads: int, value_dim: int, clear: Optional[torch.Tensor] = None, gain_per_head: bool = False,
+               gate_sigmoid: bool = False, max_row: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[t, h] = rmsnorm(o[t, h]) * gain * silu(gate[t, h]) per head of ``value_dim`` values; ``gate``: float32
-    [T, H * dv] (may be a column slice) or None."""
+    [T, H * dv] (may be a column slice) or None. ``gain_per_head``: ``gain`` is [H * dv]. ``gate_sigmoid``: the gate's
+    sigmoid instead of its silu. ``max_row`` (float32 [T, H]): ``o`` is [T, H * (dv + 1)], a head's last column being
+    its normaliser n; o[t, h] is first divided by max(|n|, exp(-max_row[t, h])) + 1e-6."""
     _want(o, "gla_finish o", torch.float32, 2)
     _want(gain, "gla_finish gain", torch.float32, 1)
     _want(out, "gla_finish out", ndim=2)
     T = o.shape[0]
-    if o.shape != (T, num_heads * value_dim) or out.shape != o.shape or gain.numel() != value_dim:
+    xs = value_dim + (1 if max_row is not None else 0)
+    if max_row is not None:
+        _want(max_row, "gla_finish max_row", torch.float32, 2)
+        if max_row.shape != (T, num_heads):
+            raise KernelError(f"gla_finish: maxima {tuple(max_row.shape)} for {T} tokens and {num_heads} heads")
+    if (o.shape != (T, num_heads * xs) or out.shape != (T, num_heads * value_dim)
+            or gain.numel() != (num_heads * value_dim if gain_per_head else value_dim)):
         raise KernelError(f"gla_finish: o {tuple(o.shape)}, out {tuple(out.shape)}, gain {tuple(gain.shape)}")
     gp, ldg = (None, 0)
     if gate is not None:
         gp, ldg = _slice(gate, "gla_finish gate")
-        if gate.shape != o.shape:
-            raise KernelError(f"gla_finish: gate {tuple(gate.shape)} does not match o {tuple(o.shape)}")
+        if gate.shape != out.shape:
+            raise KernelError(f"gla_finish: gate {tuple(gate.shape)} does not match out {tuple(out.shape)}")
     lib = library("linear_attention")
     _check(lib, lib.lp_gla_finish(o.data_ptr(), gain.data_ptr(), float(eps), gp, ldg, out.data_ptr(),
                                   _code(out, "gla_finish out"), T, num_heads, value_dim, *_clear_args(clear, "gla_finish"),
-                                  _stream()))
+                                  xs, 1 if gain_per_head else 0, 1 if gate_sigmoid else 0, _ptr(max_row), _stream()))
     return out
+
+
+def exp_gates(proj: torch.Tensor, i_off: int, f_off: int, bias_i: Optional[torch.Tensor], bias_f: Optional[torch.Tensor],
+              cap: Optional[float], mstate: torch.Tensor, slots: torch.Tensor, q_start: torch.Tensor,
+              decay: torch.Tensor, gain: torch.Tensor, max_row: torch.Tensor) -> None:
+    """Exponential gates with a running maximum, per token and head, in token order for every sequence of the step:
+    i = cap * tanh((zi + bias_i) / cap), f = logsigmoid(cap * tanh((zf + bias_f) / cap)) from the float32 columns
+    ``i_off`` / ``f_off`` of ``proj`` (H each), m_t = max(f + m_(t-1), i) from and into ``mstate`` float32 [slots, H];
+    writes decay = exp(f + m_(t-1) - m_t), gain = exp(i - m_t) and max_row = m_t, each float32 [T, H]."""
+    _want(proj, "exp_gates proj", torch.float32, 2)
+    _want(mstate, "exp_gates mstate", torch.float32, 2)
+    _want(slots, "exp_gates slots", torch.int32, 1)
+    _want(q_start, "exp_gates q_start", torch.int32, 1)
+    T, H, B = proj.shape[0], mstate.shape[1], slots.numel()
+    for name, t in (("decay", decay), ("gain", gain), ("max_row", max_row)):
+        _want(t, f"exp_gates {name}", torch.float32, 2)
+        if t.shape != (T, H):
+            raise KernelError(f"exp_gates: {name} {tuple(t.shape)} for {T} tokens and {H} heads")
+    for name, t in (("bias_i", bias_i), ("bias_f", bias_f)):
+        if t is not None:
+            _want(t, f"exp_gates {name}", torch.float32, 1)
+            if t.numel() != H:
+                raise KernelError(f"exp_gates: {name} of {t.numel()} values for {H} heads")
+    if q_start.numel() != B + 1:
+        raise KernelError(f"exp_gates: {q_start.numel()} offsets for {B} sequences")
+    lib = library("linear_attention")
+    _check(lib, lib.lp_exp_gates(proj.data_ptr(), proj.shape[1], int(i_off), int(f_off), _ptr(bias_i), _ptr(bias_f),
+                                 float(cap or 0.0), mstate.data_ptr(), slots.data_ptr(), q_start.data_ptr(),
+                                 decay.data_ptr(), gain.data_ptr(), max_row.data_ptr(), B, H, _stream()))
+
+
+# --------------------------------------------------------------------------- general attention heads, sublayer norms
+def qkv_prepare(qkv: torch.Tensor, bias: Optional[torch.Tensor], rotation: Rotation, positions: torch.Tensor,
+                seq_ids: torch.Tensor, page_table: torch.Tensor, q_out: torch.Tensor, pages: torch.Tensor, *,
+                num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, unit_norm_eps: Optional[float]) -> None:
+    """From the float32 projection ``qkv`` [T, H * dk + G * dk + G * dv]: add ``bias`` (float32, same width, or None),
+    rotate queries and keys, divide each query and key head by its root mean square (``unit_norm_eps`` not None), and
+    store queries to ``q_out`` [T, H * hdp] and keys and values into ``pages`` [num_pages, 2, G, page_size, hdp], every
+    head padded with zeros to the pages' head size hdp."""
+    _want(qkv, "qkv_prepare qkv", torch.float32, 2)
+    _want(positions, "qkv_prepare positions", torch.int32, 1)
+    _want(seq_ids, "qkv_prepare seq_ids", torch.int32, 1)
+    _want(page_table, "qkv_prepare page_table", torch.int32, 2)
+    _want(q_out, "qkv_prepare q_out", ndim=2)
+    _want(pages, "qkv_prepare pages", q_out.dtype, 5)
+    T = qkv.shape[0]
+    H, G, dk, dv = num_heads, num_kv_heads, key_dim, value_dim
+    hdp = pages.shape[4]
+    F = (H + G) * dk + G * dv
+    if qkv.shape[1] != F or q_out.shape != (T, H * hdp) or pages.shape[1] != 2 or pages.shape[2] != G:
+        raise KernelError(f"qkv_prepare: qkv {tuple(qkv.shape)}, q_out {tuple(q_out.shape)}, pages {tuple(pages.shape)}")
+    if bias is not None:
+        _want(bias, "qkv_prepare bias", torch.float32, 1)
+        if bias.numel() != F:
+            raise KernelError(f"qkv_prepare: a bias of {bias.numel()} values for {F} features")
+    freq_ptr, rotary_dim, interleaved = rotation.checked("qkv_prepare")
+    lib = library("elementwise")
+    _check(lib, lib.lp_qkv_prepare(
+        qkv.data_ptr(), qkv.shape[1], _ptr(bias), freq_ptr, positions.data_ptr(), seq_ids.data_ptr(),
+        page_table.data_ptr(), page_table.shape[1], q_out.data_ptr(), _code(q_out, "qkv_prepare q_out"), pages.data_ptr(),
+        _code(pages, "qkv_prepare pages"), T, H, G, dk, dv, hdp, rotary_dim, interleaved,
+        0 if unit_norm_eps is None else 1, float(unit_norm_eps or 0.0), pages.shape[3], _stream()))
+
+
+def post_norm_add(y: torch.Tensor, weight: torch.Tensor, eps: float, x: torch.Tensor, *, next_weight: Optional[torch.Tensor] = None,
+                  next_eps: float = 0.0, next_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x += y / sqrt(mean(y^2) + eps) * weight, float32 in place; with ``next_weight``, also
+    next_out = x / sqrt(mean(x^2) + next_eps) * next_weight of the new x (the norm in front of the next sublayer)."""
+    _want(y, "post_norm_add y", torch.float32, 2)
+    _want(x, "post_norm_add x", torch.float32, 2)
+    _want(weight, "post_norm_add weight", torch.float32, 1)
+    T, d = x.shape
+    if y.shape != x.shape or weight.numel() != d:
+        raise KernelError(f"post_norm_add: y {tuple(y.shape)}, x {tuple(x.shape)}, weight {tuple(weight.shape)}")
+    code = F32
+    if next_weight is not None:
+        _want(next_weight, "post_norm_add next_weight", torch.float32, 1)
+        _want(next_out, "post_norm_add next_out", ndim=2)
+        if next_weight.numel() != d or next_out.shape != x.shape:
+            raise KernelError(f"post_norm_add: next norm {tuple(next_weight.shape)} into {tuple(next_out.shape)}")
+        code = _code(next_out, "post_norm_add next_out")
+    lib = library("elementwise")
+    _check(lib, lib.lp_post_norm_add(y.data_ptr(), weight.data_ptr(), float(eps), x.data_ptr(), _ptr(next_weight),
+                                     float(next_eps), _ptr(next_out) if next_weight is not None else None, code, T, d,
+                                     _stream()))
+    return x
+
+
+def stream_add(x: torch.Tensor, other: Optional[torch.Tensor] = None, vector: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x[t] += other[t] + vector, float32 in place; either may be None."""
+    _want(x, "stream_add x", torch.float32, 2)
+    T, d = x.shape
+    if other is not None:
+        _want(other, "stream_add other", torch.float32, 2)
+        if other.shape != x.shape:
+            raise KernelError(f"stream_add: other {tuple(other.shape)} does not match x {tuple(x.shape)}")
+    if vector is not None:
+        _want(vector, "stream_add vector", torch.float32, 1)
+        if vector.numel() != d:
+            raise KernelError(f"stream_add: a vector of {vector.numel()} values for rows of {d}")
+    lib = library("elementwise")
+    _check(lib, lib.lp_stream_add(x.data_ptr(), _ptr(other), _ptr(vector), T, d, _stream()))
+    return x
+
+
+def relu2(z: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out = max(z, 0)^2; ``z``: float32 [T, F] (may be a column slice)."""
+    zp, ldz = _slice(z, "relu2 z")
+    _want(out, "relu2 out", ndim=2)
+    if out.shape != z.shape:
+        raise KernelError(f"relu2: z {tuple(z.shape)}, out {tuple(out.shape)}")
+    lib = library("elementwise")
+    _check(lib, lib.lp_relu2(zp, ldz, out.data_ptr(), _code(out, "relu2 out"), z.shape[0], z.shape[1], _stream()))
+    return out
+
+
+# --------------------------------------------------------------------------- routing of a mixture of experts
+def route(logits: torch.Tensor, weights: torch.Tensor, *, groups: int, keep: int, top: int) -> torch.Tensor:
+    """weights[t, e] = the weight of expert e for token t (zero if it was not chosen) from the router's float32
+    ``logits`` [T, E] (may be a column slice): scores sigmoid(logit); a group of E / groups neighbours scores the sum
+    of its two largest; the ``top`` largest scores within the ``keep`` best groups win; weights are the winners'
+    scores divided by their sum."""
+    zp, ldz = _slice(logits, "route logits")
+    _want(weights, "route weights", torch.float32, 2)
+    if weights.shape != logits.shape:
+        raise KernelError(f"route: logits {tuple(logits.shape)}, weights {tuple(weights.shape)}")
+    lib = library("routing")
+    _check(lib, lib.lp_route(zp, ldz, weights.data_ptr(), weights.shape[1], logits.shape[0], logits.shape[1], int(groups),
+                             int(keep), int(top), _stream()))
+    return weights
+
+
+def expert_scale(hidden: torch.Tensor, weights: torch.Tensor, expert_size: int) -> torch.Tensor:
+    """hidden[t, e * expert_size + j] *= weights[t, e] in place for the E experts of ``weights`` [T, E]; columns of
+    ``hidden`` beyond E * expert_size are left as they are."""
+    _want(hidden, "expert_scale hidden", ndim=2)
+    _want(weights, "expert_scale weights", torch.float32, 2)
+    T, E = weights.shape
+    if hidden.shape[0] != T or hidden.shape[1] < E * expert_size:
+        raise KernelError(f"expert_scale: hidden {tuple(hidden.shape)} for {E} experts of {expert_size}")
+    lib = library("routing")
+    _check(lib, lib.lp_expert_scale(hidden.data_ptr(), _code(hidden, "expert_scale hidden"), hidden.shape[1],
+                                    weights.data_ptr(), E, T, E, int(expert_size), _stream()))
+    return hidden
 
 
 # --------------------------------------------------------------------------- sampling

@@ -20,7 +20,7 @@ from ..errors import ConfigError
 from ..kernels import ops
 from .base import MIXERS, POSITIONS, Part, PendingNorm, Runtime
 from .linear import Linear
-from .specs import MATRIX, AttentionSpec, TensorSpec
+from .specs import BIAS, MATRIX, AttentionSpec, TensorSpec
 
 
 class Attention(Part):
@@ -34,10 +34,19 @@ class Attention(Part):
             raise ConfigError(f"attention window must be positive or absent, got {s.window}")
         if not s.shares_kv and (s.k is None or s.v is None):
             raise ConfigError("an attention layer that keeps its own cache needs key and value projections")
+        if s.general and s.shares_kv:
+            raise ConfigError("a layer with biases, unit-norm heads, capped scores, sinks or values of another size keeps its own cache")
+        if s.softcap is not None and not s.softcap > 0:
+            raise ConfigError(f"score cap must be positive or absent, got {s.softcap}")
         self.spec = spec
         self.position = POSITIONS.build(s.position)
         self.qkv: Optional[Linear] = None
         self.out: Optional[Linear] = None
+        self.value_dim = s.value_dim if s.value_dim is not None else s.head_dim
+        # the general path stores queries, keys and values with one head size, padded with zeros
+        self.stored_dim = -(-max(s.head_dim, self.value_dim) // 16) * 16 if s.general else s.head_dim
+        self.bias: Optional[torch.Tensor] = None
+        self.sinks: Optional[torch.Tensor] = None
 
     @property
     def capture_safe(self) -> bool:
@@ -51,7 +60,15 @@ class Attention(Part):
         if not s.shares_kv:
             specs[s.k] = TensorSpec((s.num_kv_heads * s.head_dim, s.hidden_size), MATRIX)
             specs[s.v] = TensorSpec((s.num_kv_heads * s.head_dim, s.hidden_size), MATRIX)
-        specs[s.o] = TensorSpec((s.hidden_size, s.num_heads * s.head_dim), MATRIX)
+        specs[s.o] = TensorSpec((s.hidden_size, s.num_heads * self.value_dim), MATRIX)
+        if not s.shares_kv:
+            specs[s.v] = TensorSpec((s.num_kv_heads * self.value_dim, s.hidden_size), MATRIX)
+        for name, rows in ((s.q_bias, s.num_heads * s.head_dim), (s.k_bias, s.num_kv_heads * s.head_dim),
+                           (s.v_bias, s.num_kv_heads * self.value_dim)):
+            if name is not None:
+                specs[name] = TensorSpec((rows,), BIAS)
+        if s.sink is not None:
+            specs[s.sink] = TensorSpec((s.num_heads,), BIAS)
         return specs
 
     def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
@@ -59,15 +76,28 @@ class Attention(Part):
         s = self.spec
         names = [s.q] if s.shares_kv else [s.q, s.k, s.v]
         self.qkv = Linear([tensors[n] for n in names], runtime)      # rows: queries, keys, values
-        self.out = Linear([tensors[s.o]], runtime)
+        o = tensors[s.o]
+        if self.stored_dim != self.value_dim:
+            # the attention kernels leave heads of stored_dim values (zeros beyond value_dim): give `o` columns to match
+            wide = torch.zeros((o.shape[0], s.num_heads, self.stored_dim), dtype=o.dtype)
+            wide[:, :, :self.value_dim] = o.view(o.shape[0], s.num_heads, self.value_dim)
+            o = wide.view(o.shape[0], s.num_heads * self.stored_dim)
+        self.out = Linear([o], runtime)
         self.position.load(tensors, runtime)
+        if any(b is not None for b in (s.q_bias, s.k_bias, s.v_bias)):
+            parts = [(s.q_bias, s.num_heads * s.head_dim), (s.k_bias, s.num_kv_heads * s.head_dim),
+                     (s.v_bias, s.num_kv_heads * self.value_dim)]
+            self.bias = torch.cat([tensors[n].to(torch.float32) if n is not None else torch.zeros(rows)
+                                   for n, rows in parts]).to(runtime.device).contiguous()
+        if s.sink is not None:
+            self.sinks = runtime.gain(tensors[s.sink])
 
     # ------------------------------------------------------------------ cache
     def cache_request(self):
         s = self.spec
         if s.shares_kv:
             return None
-        return KVRequest(s.num_kv_heads, s.head_dim, s.window)
+        return KVRequest(s.num_kv_heads, self.stored_dim, s.window)
 
     # ------------------------------------------------------------------ step
     def buffer_to_clear(self, ctx, tokens: int):
@@ -98,12 +128,41 @@ class Attention(Part):
         with ops.section("attention.out"):
             self.out.few(o, residual, ops.ACCUMULATE, zero=sums[:ops.FEW_TOKENS + T * F])
 
+    def _forward_general(self, ctx, cache, x, residual: torch.Tensor, then_norm=None) -> bool:
+        """A layer with biases, unit-norm heads, capped scores, sinks or values of another size than its keys:
+        projection with float32 sums, one kernel that adds the biases, rotates, norms and stores queries, keys and
+        values (heads padded to ``stored_dim``), then the attention kernels with the cap and the sinks as arguments."""
+        s, rt = self.spec, self.runtime
+        if isinstance(x, PendingNorm):
+            x = x.tensor()
+        T = x.shape[0]
+        H, G, hd = s.num_heads, s.num_kv_heads, self.stored_dim
+        rotation = self.position.rotation()
+        if rotation is None:
+            raise ConfigError("the general attention path applies rotations only (a position part with rotation())")
+        table = ctx.page_tables[cache.group_index]
+        qkv = ctx.buffer("qkv", (T, self.qkv.out_features), torch.float32)
+        with ops.section("attention.qkv"):
+            self.qkv.store(x, qkv, ctx)
+        q = ctx.buffer("q", (T, H * hd), rt.act_dtype)
+        with ops.section("attention.position"):
+            ops.qkv_prepare(qkv, self.bias, rotation, ctx.positions, ctx.seq_ids, table, q, cache.pages, num_heads=H,
+                            num_kv_heads=G, key_dim=s.head_dim, value_dim=self.value_dim, unit_norm_eps=s.unit_norm_eps)
+        o = ctx.buffer("attn_out", (T, H * hd), rt.act_dtype)
+        with ops.section("attention.scores"):
+            ops.attention(ctx, q, o, cache.pages, table, num_heads=H, num_kv_heads=G, head_dim=hd, scale=s.scale,
+                          window=s.window, fast=rt.fast, softcap=s.softcap, sinks=self.sinks)
+        with ops.section("attention.out"):
+            return self.out.accumulate(o, residual, ctx, then_norm)
+
     def forward(self, ctx, cache, x, residual: torch.Tensor, then_norm=None) -> bool:
         """Adds the layer's output into ``residual``; returns whether ``then_norm`` was fused.
         ``x``: the normed stream, or a :class:`PendingNorm` of it."""
         s, rt = self.spec, self.runtime
         if cache is None:
             raise ConfigError("attention needs a key/value cache (its own or another run's)")
+        if s.general:
+            return self._forward_general(ctx, cache, x, residual, then_norm)
         H, G, hd = s.num_heads, s.num_kv_heads, s.head_dim
         # the position encoding as something the kernels do on the way (a rotation), or None: then the
         # encoding's own part changes queries and keys in the projection's output before the kernels run

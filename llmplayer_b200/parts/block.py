@@ -17,7 +17,7 @@ from ..kernels import ops
 from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, FollowingNorm, Part, PendingNorm, Runtime
 from ..errors import ConfigError
 from .linear import Linear
-from .specs import BIAS, MATRIX, BlockSpec, ParallelBlockSpec, TensorSpec
+from .specs import BIAS, MATRIX, BlockSpec, ParallelBlockSpec, SandwichBlockSpec, TensorSpec
 
 
 class PreNormBlock(Part):
@@ -240,5 +240,72 @@ class ParallelBlock(Part):
         return False
 
 
+class SandwichBlock(Part):
+    """x += post_norm(mixer(norm(x))); x += post_norm(ffn(norm(x))): a norm in front of and behind each sublayer.
+    A sublayer adds its result into a zeroed float32 buffer; one kernel then norms that result, adds it into the
+    stream and, when a further sublayer of this layer follows, writes that sublayer's input norm in the same pass.
+    The norms are RMS norms (the kernel's rule); the feed-forward may be absent."""
+
+    def __init__(self, spec: SandwichBlockSpec):
+        self.spec = spec
+        if (spec.ffn is None) != (spec.ffn_norm is None) or (spec.ffn is None) != (spec.post_ffn_norm is None):
+            raise ConfigError("a feed-forward comes with the norms in front of and behind it, or not at all")
+        self.mixer_norm = NORMS.build(spec.mixer_norm)
+        self.mixer = MIXERS.build(spec.mixer)
+        self.post_mixer_norm = NORMS.build(spec.post_mixer_norm)
+        self.ffn_norm = NORMS.build(spec.ffn_norm) if spec.ffn is not None else None
+        self.ffn = FEED_FORWARDS.build(spec.ffn) if spec.ffn is not None else None
+        self.post_ffn_norm = NORMS.build(spec.post_ffn_norm) if spec.ffn is not None else None
+        for norm in (self.mixer_norm, self.post_mixer_norm, self.ffn_norm, self.post_ffn_norm):
+            if norm is not None and not getattr(norm, "fusable_rms", False):
+                raise ConfigError("the norms of a sandwich block are RMS norms")
+
+    def children(self):
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.post_mixer_norm, self.ffn_norm, self.ffn,
+                                 self.post_ffn_norm) if p is not None)
+
+    @property
+    def capture_safe(self) -> bool:
+        return all(bool(getattr(part, "capture_safe", False)) for part in self.children())
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        out: Dict[str, TensorSpec] = {}
+        for part in self.children():
+            out.update(part.tensor_specs())
+        return out
+
+    def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
+        super().load(tensors, runtime)
+        for part in self.children():
+            part.load(tensors, runtime)
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
+    def forward(self, ctx, cache, residual: torch.Tensor) -> bool:
+        act = self.runtime.act_dtype
+        h = ctx.buffer("normed", tuple(residual.shape), act)
+        y = ctx.buffer("sublayer_out", tuple(residual.shape), torch.float32)
+        with ops.section("norm"):
+            self.mixer_norm.apply(residual, h)
+            y.zero_()
+        self.mixer.forward(ctx, cache, h, y)
+        post = self.post_mixer_norm
+        with ops.section("norm"):
+            if self.ffn is None:
+                ops.post_norm_add(y, post.weight, post.spec.eps, residual)
+                return False
+            nxt = self.ffn_norm
+            ops.post_norm_add(y, post.weight, post.spec.eps, residual, next_weight=nxt.weight, next_eps=nxt.spec.eps,
+                              next_out=h)
+            y.zero_()
+        self.ffn.forward(ctx, h, y)
+        post = self.post_ffn_norm
+        with ops.section("norm"):
+            ops.post_norm_add(y, post.weight, post.spec.eps, residual)
+        return False
+
+
+BLOCKS.register("sandwich", SandwichBlock)
 BLOCKS.register("prenorm", PreNormBlock)
 BLOCKS.register("parallel", ParallelBlock)

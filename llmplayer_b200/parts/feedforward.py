@@ -12,9 +12,10 @@ from typing import Dict, Mapping, Optional
 
 import torch
 
+from ..errors import ConfigError
 from .base import FEED_FORWARDS, Part, PendingNorm, Runtime
 from .linear import Linear
-from .specs import BIAS, MATRIX, SwiGLUSpec, TensorSpec, XIELUSpec
+from .specs import BIAS, MATRIX, MixtureSpec, SquaredReLUSpec, SwiGLUSpec, TensorSpec, XIELUSpec
 
 
 class SwiGLU(Part):
@@ -137,3 +138,119 @@ class XIELUFeedForward(Part):
 
 
 FEED_FORWARDS.register("xielu", XIELUFeedForward)
+
+
+class SquaredReLU(Part):
+    """down(relu(up x)^2); the activation is evaluated in float32 on the float32 sums of the up projection."""
+    capture_safe = True
+
+    def __init__(self, spec: SquaredReLUSpec):
+        self.spec = spec
+        self.up: Optional[Linear] = None
+        self.down: Optional[Linear] = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        s = self.spec
+        return {s.up: TensorSpec((s.intermediate_size, s.hidden_size), MATRIX),
+                s.down: TensorSpec((s.hidden_size, s.intermediate_size), MATRIX)}
+
+    def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
+        super().load(tensors, runtime)
+        self.up = Linear([tensors[self.spec.up]], runtime)
+        self.down = Linear([tensors[self.spec.down]], runtime)
+
+    def forward(self, ctx, x, residual: torch.Tensor) -> bool:
+        from ..kernels import ops
+        if isinstance(x, PendingNorm):
+            x = x.tensor()
+        T, F = x.shape[0], self.spec.intermediate_size
+        z = ctx.buffer("ffn_up", (T, F), torch.float32)
+        with ops.section("ffn.up"):
+            self.up.store(x, z, ctx)
+        h = ctx.buffer("ffn_hidden", (T, F), self.runtime.act_dtype)
+        with ops.section("ffn.act"):
+            ops.relu2(z, h)
+        with ops.section("ffn.down"):
+            self.down.accumulate(h, residual, ctx)
+        return False
+
+
+FEED_FORWARDS.register("squared_relu", SquaredReLU)
+
+
+class Mixture(Part):
+    """Mixture of gated experts. The router's logits are a product with float32 sums; the routing kernel turns them
+    into one weight per token and expert (zero where the token did not choose the expert). The experts run as ONE
+    stacked gated product over all of them (gate and up matrices of every expert, and of the shared expert, stacked
+    by rows), whose hidden activations are multiplied by the token's weight for their expert, and ONE down product
+    over the experts' down matrices stacked by columns, which sums the weighted outputs: every token passes through
+    every expert, so the cost does not depend on the routing and the step has no host-side decisions (it replays
+    from a captured graph); what a token did not choose is multiplied by zero."""
+    capture_safe = True
+
+    def __init__(self, spec: MixtureSpec):
+        s, r = spec, spec.routing
+        if r.num_experts <= 0 or r.groups <= 0 or r.num_experts % r.groups:
+            raise ConfigError(f"{r.num_experts} experts cannot form {r.groups} equal groups")
+        if not 0 < r.keep_groups <= r.groups:
+            raise ConfigError(f"{r.keep_groups} of {r.groups} groups kept")
+        if not 0 < r.top <= r.keep_groups * (r.num_experts // r.groups):
+            raise ConfigError(f"{r.top} experts cannot be chosen from {r.keep_groups} groups of {r.num_experts // r.groups}")
+        if s.expert_size <= 0 or s.shared_size < 0 or (s.shared_size > 0 and not s.shared_prefix):
+            raise ConfigError(f"experts of {s.expert_size}, a shared expert of {s.shared_size}")
+        self.spec = spec
+        self.router: Optional[Linear] = None
+        self.gate_up: Optional[Linear] = None
+        self.down: Optional[Linear] = None
+
+    def _experts(self):
+        s = self.spec
+        names = [(f"{s.expert_prefix}e{e}.", s.expert_size) for e in range(s.routing.num_experts)]
+        if s.shared_size > 0:
+            names.append((s.shared_prefix, s.shared_size))
+        return names
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        s = self.spec
+        out: Dict[str, TensorSpec] = {}
+        for prefix, size in self._experts():
+            out[prefix + "gate"] = TensorSpec((size, s.hidden_size), MATRIX)
+            out[prefix + "up"] = TensorSpec((size, s.hidden_size), MATRIX)
+            out[prefix + "down"] = TensorSpec((s.hidden_size, size), MATRIX)
+        out[s.routing.router] = TensorSpec((s.routing.num_experts, s.hidden_size), MATRIX)
+        return out
+
+    def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
+        super().load(tensors, runtime)
+        s = self.spec
+        experts = self._experts()
+        gate = torch.cat([tensors[p + "gate"] for p, _ in experts], dim=0)
+        up = torch.cat([tensors[p + "up"] for p, _ in experts], dim=0)
+        down = torch.cat([tensors[p + "down"] for p, _ in experts], dim=1).contiguous()
+        self.total = gate.shape[0]
+        self.router = Linear([tensors[s.routing.router]], runtime)
+        self.gate_up = Linear([gate, up], runtime, gated=True)
+        self.down = Linear([down], runtime)
+
+    def forward(self, ctx, x, residual: torch.Tensor) -> bool:
+        from ..kernels import ops
+        s, r = self.spec, self.spec.routing
+        if isinstance(x, PendingNorm):
+            x = x.tensor()
+        T = x.shape[0]
+        logits = ctx.buffer("router_logits", (T, r.num_experts), torch.float32)
+        with ops.section("ffn.router"):
+            self.router.store(x, logits, ctx)
+            weights = ctx.buffer("router_weights", (T, r.num_experts), torch.float32)
+            ops.route(logits, weights, groups=r.groups, keep=r.keep_groups, top=r.top)
+        h = ctx.buffer("ffn_hidden", (T, self.total), self.runtime.act_dtype)
+        with ops.section("ffn.gate_up"):
+            self.gate_up.swiglu(x, h, ctx)
+        with ops.section("ffn.weights"):
+            ops.expert_scale(h, weights, s.expert_size)
+        with ops.section("ffn.down"):
+            self.down.accumulate(h, residual, ctx)
+        return False
+
+
+FEED_FORWARDS.register("mixture", Mixture)

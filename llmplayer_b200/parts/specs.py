@@ -97,6 +97,19 @@ class AttentionSpec:
     window: Optional[int] = None
     shares_kv: bool = False
     kind: str = "attention"
+    # What a layer may have beyond that (a layer with any of these takes the general path of the mixer):
+    value_dim: Optional[int] = None      # size of a value head when it differs from head_dim (``o`` is [hidden, heads * value_dim])
+    q_bias: Optional[str] = None         # additive vectors of the three projections
+    k_bias: Optional[str] = None
+    v_bias: Optional[str] = None
+    unit_norm_eps: Optional[float] = None    # after the rotation, queries and keys are divided by their root mean square per head
+    softcap: Optional[float] = None      # score <- softcap * tanh(score / softcap), after the scale
+    sink: Optional[str] = None           # tensor [heads]: a learned logit per head in the softmax's denominator, without key or value
+
+    @property
+    def general(self) -> bool:
+        return (self.value_dim not in (None, self.head_dim) or any(b is not None for b in (self.q_bias, self.k_bias, self.v_bias))
+                or self.unit_norm_eps is not None or self.softcap is not None or self.sink is not None)
 
 
 @dataclass(frozen=True)
@@ -170,6 +183,69 @@ class GatedLinearAttentionSpec:
 
 
 @dataclass(frozen=True)
+class MatrixMemorySpec:
+    """A matrix memory per head with exponential gates and a running maximum (the mLSTM of the xLSTM family):
+    with i = cap * tanh((W_i x + b_i) / cap), f = logsigmoid(cap * tanh((W_f x + b_f) / cap)) per head,
+    m_t = max(f + m_(t-1), i) (m starts at ``0``), S_t = exp(f + m_(t-1) - m_t) S_(t-1) + exp(i - m_t) k v^T, n_t the same
+    with k alone, and o = S_t^T q / (max(|n_t . q|, exp(-m_t)) + 1e-6) with q scaled by ``key_dim`` ** -0.5. Each head's o
+    is divided by its root mean square, the heads are multiplied by the gain ``out_norm`` [heads * value_dim] and by
+    sigmoid(``gate`` x), and projected by ``o``. ``gate_cap`` None: the gates' pre-activations are not capped."""
+    hidden_size: int
+    num_heads: int
+    key_dim: int
+    value_dim: int
+    norm_eps: float
+    gate_cap: Optional[float]
+    q: str
+    k: str
+    v: str
+    gate: str
+    input_gate: str
+    input_gate_bias: str
+    forget_gate: str
+    forget_gate_bias: str
+    out_norm: str
+    o: str
+    kind: str = "matrix_memory"
+
+
+@dataclass(frozen=True)
+class SquaredReLUSpec:
+    """Dense feed-forward down(relu(up x)^2)."""
+    hidden_size: int
+    intermediate_size: int
+    up: str
+    down: str
+    kind: str = "squared_relu"
+
+
+@dataclass(frozen=True)
+class ExpertRoutingSpec:
+    """How a token chooses its experts: scores sigmoid(router x); the experts form ``groups`` equal groups of
+    neighbours whose score is the sum of their two largest scores; only experts of the ``keep_groups`` best groups
+    may be chosen; the ``top`` largest scores among those win, and their weights are the scores divided by their sum."""
+    num_experts: int
+    top: int
+    groups: int
+    keep_groups: int
+    router: str
+
+
+@dataclass(frozen=True)
+class MixtureSpec:
+    """Mixture of gated experts down(silu(gate x) * (up x)) without biases. Expert e's tensors are
+    ``expert_prefix`` + ``e<e>.`` + gate / up / down. ``shared_size`` > 0: one more expert of that size
+    (``shared_prefix`` + gate / up / down) runs for every token with weight one."""
+    hidden_size: int
+    expert_size: int
+    routing: ExpertRoutingSpec
+    expert_prefix: str
+    shared_size: int = 0
+    shared_prefix: Optional[str] = None
+    kind: str = "mixture"
+
+
+@dataclass(frozen=True)
 class XIELUSpec:
     """Dense feed-forward down(act(up x)) with the xIELU activation, whose two learned numbers are the
     tensor ``act`` [2]."""
@@ -212,6 +288,20 @@ class ParallelBlockSpec:
 
 
 @dataclass(frozen=True)
+class SandwichBlockSpec:
+    """One layer with a norm in front of and behind each sublayer:
+    x += post_mixer_norm(mixer(mixer_norm(x))); x += post_ffn_norm(ffn(ffn_norm(x))). ``ffn`` may be None (then the
+    two norms around it are None as well)."""
+    mixer_norm: NormSpec
+    mixer: object
+    post_mixer_norm: NormSpec
+    ffn_norm: Optional[NormSpec] = None
+    ffn: Optional[object] = None
+    post_ffn_norm: Optional[NormSpec] = None
+    kind: str = "sandwich"
+
+
+@dataclass(frozen=True)
 class BlockSpec:
     """One layer: how its norms, mixer and feed-forward are arranged.
 
@@ -251,6 +341,11 @@ class ScheduleEntry:
     of the schedule whose cache this run attends over instead of keeping its own."""
     layer: int
     reads_cache_of: Optional[int] = None
+    # Before the run, added to the stream: the embedding's output (the stream as it entered the first run), and row
+    # ``add_row`` of the float32 tensor ``add_vector`` [rows, hidden] (a learned vector per pass of a repeated span)
+    add_embedding: bool = False
+    add_vector: Optional[str] = None
+    add_row: int = 0
 
 
 @dataclass(frozen=True)
