@@ -1,0 +1,156 @@
+"""Small Botuvik configurations with sizes of their own, and seeded model folders for them."""
+import json
+import os
+
+import torch
+
+# Odd sizes: values wider than keys (heads are stored padded), a rotation over part of a head, a looped span in the
+# middle, a layer without a feed-forward, groups of one expert with every group kept, no shared expert, one head.
+SMALL = {
+    "architecture": "Botuvik", "vocab": 211, "width": 72, "norm": {"eps": 2e-6},
+    "loop": {"start": 1, "stop": 3, "times": 2},
+    "layers": [
+        {"type": "attention",
+         "mixer": {"heads": 4, "kv_heads": 2, "dim": 24, "vdim": 40, "scale": 0.5, "softcap": 8.0,
+                   "rot": {"base": 10000.0, "dims": 16}},
+         "mlp": {"kind": "moe", "expert": {"ff": 24}, "shared": {"ff": 40},
+                 "router": {"experts": 6, "top": 2, "groups": {"count": 3, "keep": 2}}}},
+        {"type": "mlstm", "mixer": {"heads": 3, "dim": 10, "vdim": 28, "gate_cap": 6.0},
+         "mlp": {"kind": "dense", "ff": 104}},
+        {"type": "attention",
+         "mixer": {"heads": 3, "kv_heads": 3, "dim": 16, "vdim": 16, "scale": 0.7, "softcap": 30.0,
+                   "rot": {"base": 300.0, "dims": 16}},
+         "mlp": None},
+        {"type": "mlstm", "mixer": {"heads": 1, "dim": 36, "vdim": 20, "gate_cap": 15.0},
+         "mlp": {"kind": "moe", "expert": {"ff": 16}, "shared": None,
+                 "router": {"experts": 4, "top": 1, "groups": {"count": 4, "keep": 4}}}},
+    ],
+}
+# Sizes the tensor-core kernels take (heads of 64 and 128, keys wider than values), a loop over the first layer alone,
+# eight query heads on one key head, one group kept of two.
+WIDE = {
+    "architecture": "Botuvik", "vocab": 384, "width": 128, "norm": {"eps": 1e-5},
+    "loop": {"start": 0, "stop": 1, "times": 3},
+    "layers": [
+        {"type": "mlstm", "mixer": {"heads": 2, "dim": 64, "vdim": 128, "gate_cap": 10.0},
+         "mlp": {"kind": "dense", "ff": 256}},
+        {"type": "attention",
+         "mixer": {"heads": 8, "kv_heads": 1, "dim": 64, "vdim": 64, "scale": 0.2, "softcap": 50.0,
+                   "rot": {"base": 1000000.0, "dims": 32}},
+         "mlp": {"kind": "moe", "expert": {"ff": 64}, "shared": {"ff": 128},
+                 "router": {"experts": 8, "top": 3, "groups": {"count": 2, "keep": 1}}}},
+        {"type": "attention",
+         "mixer": {"heads": 2, "kv_heads": 2, "dim": 128, "vdim": 64, "scale": 0.09, "softcap": 5.0,
+                   "rot": {"base": 10000.0, "dims": 128}},
+         "mlp": {"kind": "dense", "ff": 128}},
+    ],
+}
+# A width that is no multiple of 8 (every product leaves the tensor cores, also in bfloat16), no loop at all,
+# one expert chosen of two groups of two, a head without rotation.
+RAGGED = {
+    "architecture": "Botuvik", "vocab": 131, "width": 52, "norm": {"eps": 3e-5},
+    "layers": [
+        {"type": "mlstm", "mixer": {"heads": 2, "dim": 6, "vdim": 70, "gate_cap": 4.0},
+         "mlp": {"kind": "moe", "expert": {"ff": 12}, "shared": {"ff": 20},
+                 "router": {"experts": 4, "top": 1, "groups": {"count": 2, "keep": 1}}}},
+        {"type": "attention",
+         "mixer": {"heads": 5, "kv_heads": 1, "dim": 10, "vdim": 12, "scale": 0.4, "softcap": 3.0,
+                   "rot": {"base": 100.0, "dims": 0}},
+         "mlp": {"kind": "dense", "ff": 60}},
+    ],
+}
+CONFIGS = {"small": (SMALL, 21, 0.09), "wide": (WIDE, 22, 0.06), "ragged": (RAGGED, 23, 0.1)}
+
+# bfloat16: at most four times the worst error the comparisons of each configuration achieved on a B200 (small: 5.8e-2
+# over six runs of layers whose every sublayer is normed to unit size before it is added; wide 3.3e-2; ragged 1.6e-2)
+BFLOAT16_BOUND = {"small": 8e-2, "wide": 5e-2, "ragged": 4e-2}
+ROUTE_CHANNELS = 8          # channels of the stream that carry each token's routing code (see make_model)
+
+
+def bound(dtype, name):
+    return 2e-5 if dtype == "float32" else BFLOAT16_BOUND[name]
+
+
+def make_model(tmp_path, name, dtype="bfloat16"):
+    """A model folder for configuration ``name``: the library's seeded writer, then
+
+    * the tensors whose random draw around zero would switch a mechanism off are drawn again: sinks, biases of the
+      projections and of the gates, the vectors of the loop's passes;
+    * the routing is made robust against rounding: the first ROUTE_CHANNELS channels of the stream carry a code per
+      token (distinct levels with wide gaps, in the embedding), nothing else writes to these channels (the rows of
+      every matrix that writes to the stream and the loop's vectors are zero there), and every router reads only
+      them, one channel per expert. An expert's score then depends on the token alone, up to the common factor of
+      the norm, so no choice of experts rests on a close call and bfloat16 runs choose as float64 does.
+    * a matrix memory's output is S^T q divided by its own root mean square, so early in a sequence, where S holds
+      little more than the token's own k v^T, its SIGN is the sign of q . k: with unrelated random query and key maps
+      that product is near zero every so often and the output then rests on rounding. The query maps are therefore
+      drawn as the key maps plus a third of a random matrix.
+    """
+    from llmplayer_b200.config import config_from_dict
+    from llmplayer_b200.weights import write_random_model
+    from llmplayer_b200.weights.safetensors_io import write_safetensors
+    from plain_llama import read_safetensors
+    raw, seed, std = CONFIGS[name]
+    out = os.path.join(str(tmp_path), f"botuvik_{name}_{dtype}")
+    write_random_model(config_from_dict(raw), seed, out, dtype=dtype, std=std)
+    path = os.path.join(out, "model.safetensors")
+    tensors = read_safetensors(path)
+    gen = torch.Generator().manual_seed(seed + 100)
+    store = torch.bfloat16 if dtype == "bfloat16" else torch.float32
+    d, C = raw["width"], ROUTE_CHANNELS
+
+    def draw(*shape, scale=1.0, shift=0.0):
+        return (shift + scale * torch.randn(*shape, generator=gen)).to(store)
+
+    # a token's code: a permutation of levels whose values, and whose sums of two, are all at least 0.09 apart
+    levels = torch.tensor([-1.88, -1.69, -1.49, -0.09, 0.01, 0.82, 1.3, 1.95])
+    embed = tensors["embed"].to(torch.float32)
+    for t in range(raw["vocab"]):
+        embed[t, :C] = levels[torch.randperm(C, generator=gen)] * (0.6 + 0.4 * torch.rand(1, generator=gen))
+    tensors["embed"] = embed.to(store)
+    if "loop" in raw:
+        step = draw(raw["loop"]["times"], d, scale=0.4).to(torch.float32)
+        step[:, :C] = 0
+        tensors["loop.step"] = step.to(store)
+    for i, layer in enumerate(raw["layers"]):
+        p, m = f"l{i}.", layer["mixer"]
+        writers = [p + "mix.o"]
+        if layer["type"] == "attention":
+            tensors[p + "mix.sink"] = draw(m["heads"], scale=2.0)
+            tensors[p + "mix.q.b"] = draw(m["heads"] * m["dim"], scale=0.3)
+            tensors[p + "mix.k.b"] = draw(m["kv_heads"] * m["dim"], scale=0.3)
+            tensors[p + "mix.v.b"] = draw(m["kv_heads"] * m["vdim"], scale=0.3)
+        else:
+            tensors[p + "mix.i.b"] = draw(m["heads"], scale=1.0)
+            tensors[p + "mix.f.b"] = draw(m["heads"], scale=2.0, shift=2.0)
+            tensors[p + "mix.i"] = draw(m["heads"], d, scale=0.4)
+            tensors[p + "mix.f"] = draw(m["heads"], d, scale=0.4)
+            # the query map is tied to the key map, so that a token's own q . k is clearly positive (see make_model)
+            tensors[p + "mix.q"] = (tensors[p + "mix.k"].to(torch.float32) + 0.3 * tensors[p + "mix.q"].to(torch.float32)).to(store)
+        mlp = layer["mlp"]
+        if mlp is not None and mlp["kind"] == "dense":
+            writers.append(p + "mlp.down")
+        elif mlp is not None:
+            E = mlp["router"]["experts"]
+            assert E <= C
+            router = torch.zeros(E, d)
+            router[torch.arange(E), torch.arange(E)] = 1.0
+            tensors[p + "mlp.router"] = router.to(store)
+            tensors[p + "norm2"] = torch.cat([torch.ones(C), tensors[p + "norm2"][C:].to(torch.float32)]).to(store)
+            writers += [f"{p}mlp.e{e}.down" for e in range(E)]
+            if mlp.get("shared"):
+                writers.append(p + "mlp.shared.down")
+        for name_ in writers:
+            mat = tensors[name_].to(torch.float32)
+            mat[:C, :] = 0
+            tensors[name_] = mat.to(store)
+    write_safetensors(path, tensors, metadata={"format": "pt"})
+    with open(os.path.join(out, "config.json"), "w") as fh:
+        json.dump(raw, fh, indent=1)
+    return out
+
+
+def plain_logits(model_dir, tokens, rows=None, gaps=None):
+    import plain_botuvik
+    cfg, w = plain_botuvik.read_model(model_dir)
+    return plain_botuvik.forward(cfg, w, tokens, dtype=torch.float64, rows=rows, gaps=gaps)
