@@ -3,6 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--shape 1b|3b|8b]
     python bench.py --design ramupel [--size s|m|l] [--layers N]      (the hybrid design beside Llama at equal size)
+    python bench.py --design botuvik [--size s|m|l] [--layers N]      (the same for the Botuvik design, beside both)
 
 One "step" is one decode step of the whole batch. The default run has the Llama-3.2-1B shape, a batch of 8
 sequences with 512-token prompts in a cache sized for a context of 4096. Every figure comes from the library's
@@ -24,6 +25,8 @@ and 256 steps; batch 32 with 2,048-token prompts and 512 steps) unless ``--steps
 and decode (batch 8 from 512-token prompts) throughput of the Ramupel design at a few layer sizes, beside a Llama of
 the same width, depth, head count and feed-forward parameters, both with random weights, plus the device time per
 section of the model walk of each and what the mixers' core kernels reach of their rooflines.
+``--design botuvik`` does the same for the Botuvik design (matrix-memory layers, capped attention with sinks, dense
+and routed feed-forwards) beside Ramupel, the closest existing design (a recurrence among attention layers), and Llama.
 """
 from __future__ import annotations
 
@@ -169,6 +172,22 @@ def hybrid_configs(size, layers):
     return ramupel, llama
 
 
+def botuvik_config(size, layers):
+    """Every fourth layer a matrix memory, the others capped attention with a sink (grouped as in the Llama beside
+    it); dense and routed feed-forwards alternate (8 experts of a quarter of the dense width in 4 groups, 2 of 2 groups
+    chosen, plus a shared expert of that size)."""
+    width, heads, _, (gh, gk, gv), ff = HYBRID_SIZES[size]
+    hd = width // heads
+    attention = {"type": "attention", "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": hd, "vdim": hd,
+                                                "scale": hd ** -0.5 * 4.0, "softcap": 30.0, "rot": {"base": 10000.0, "dims": hd}}}
+    memory = {"type": "mlstm", "mixer": {"heads": gh, "dim": gk, "vdim": gv, "gate_cap": 15.0}}
+    dense = {"kind": "dense", "ff": ff}
+    routed = {"kind": "moe", "expert": {"ff": ff // 4}, "shared": {"ff": ff // 4},
+              "router": {"experts": 8, "top": 2, "groups": {"count": 4, "keep": 2}}}
+    return {"architecture": "Botuvik", "vocab": 32000, "width": width, "norm": {"eps": 1e-5},
+            "layers": [dict(memory if i % 4 == 0 else attention, mlp=routed if i % 2 else dense) for i in range(layers)]}
+
+
 def compare_designs(args, peaks) -> int:
     import torch
     from llmplayer_b200 import Engine
@@ -184,12 +203,17 @@ def compare_designs(args, peaks) -> int:
     gen = torch.Generator().manual_seed(5)
     clocks = ClockSampler()
     clocks.start()
-    out = {"metric": "prefill and decode tok/s of the Ramupel design beside Llama at equal size (bf16)", "impl": "ours",
+    botuvik = args.design == "botuvik"
+    out = {"metric": f"prefill and decode tok/s of the {'Botuvik' if botuvik else 'Ramupel'} design beside "
+                     f"{'Ramupel and ' if botuvik else ''}Llama at equal size (bf16)", "impl": "ours",
            "layers": layers, "batch": batch, "prompt_len": prompt, "prefill_len": prefill_len, "peaks": peaks, "sizes": {}}
     try:
         for size in ([args.size] if args.size else sorted(HYBRID_SIZES, key="sml".index)):
             row = {}
-            for name, raw in zip(("ramupel", "llama"), hybrid_configs(size, layers)):
+            designs = list(zip(("ramupel", "llama"), hybrid_configs(size, layers)))
+            if botuvik:
+                designs.insert(0, ("botuvik", botuvik_config(size, layers)))
+            for name, raw in designs:
                 vocab = raw.get("vocab", raw.get("vocab_size"))
                 tmp = tempfile.mkdtemp(prefix="llmplayer_b200_bench_")
                 try:
@@ -250,6 +274,8 @@ def compare_designs(args, peaks) -> int:
                 del engine, profiled
                 torch.cuda.empty_cache()
             row["rooflines"] = hybrid_rooflines(size, layers, row, peaks, batch, prompt + 10, prefill_len)
+            if botuvik:
+                row["rooflines"].update(botuvik_rooflines(size, layers, row, peaks, batch, prompt + 10, prefill_len))
             out["sizes"][size] = row
         print(json.dumps(out))
         return 0
@@ -288,6 +314,34 @@ def hybrid_rooflines(size, layers, row, peaks, batch, context, n):
     return out
 
 
+def botuvik_rooflines(size, layers, row, peaks, batch, context, n):
+    """The Botuvik kernels that have no twin in the products (which are the same kernels for every design): prompt
+    kernels against the bf16 tensor peak, decode kernels against the copy bandwidth."""
+    width, heads, _, (gh, gk, gv), ff = HYBRID_SIZES[size]
+    n_mem = sum(1 for i in range(layers) if i % 4 == 0)
+    n_att = layers - n_mem
+    n_routed = sum(1 for i in range(layers) if i % 2)
+    flops, gbs = peaks["bf16_tflops"] * 1e12, peaks["hbm_gbs"] * 1e9
+    b = row["botuvik"]
+    hd, G = width // heads, max(1, heads // 4)
+
+    def frac(work, ms, count, peak):
+        return None if not ms or not count else work / (ms / count / 1e3) / peak
+    routed_rows = 8 * (ff // 4) + ff // 4
+    return {
+        "prefill botuvik attention (of tensor peak)": frac(
+            heads * n * (n + 1) * 2 * hd, b["prefill_sections_ms"].get("attention.scores"), n_att, flops),
+        "prefill botuvik recurrence (of tensor peak)": frac(
+            6.0 * gh * gk * (gv + 1) * n, b["prefill_sections_ms"].get("recurrence.scan"), n_mem, flops),
+        "prefill botuvik routed gate/up product, all experts (of tensor peak)": frac(
+            2.0 * n * width * 2 * routed_rows, b["prefill_sections_ms"].get("ffn.gate_up"), n_routed, flops),
+        "decode botuvik attention (of copy bandwidth)": frac(
+            batch * context * 2 * G * hd * 2, b["decode_sections_ms"].get("attention.scores"), n_att, gbs),
+        "decode botuvik recurrence (of copy bandwidth)": frac(
+            batch * gh * gk * (gv + 1) * 4 * 2, b["decode_sections_ms"].get("recurrence.scan"), n_mem, gbs),
+    }
+
+
 def spread(values):
     return {"median": statistics.median(values), "min": min(values), "max": max(values), "repeats": len(values)}
 
@@ -308,9 +362,10 @@ def main() -> int:
     ap.add_argument("--prefill-only", action="store_true",
                     help="measure only the 2,048-token prefill (small runs for profiling)")
     ap.add_argument("--profile", action="store_true", help="add the device time per section of the model walk")
-    ap.add_argument("--design", default="llama", choices=("llama", "ramupel"),
-                    help="ramupel: the hybrid design beside Llama at equal size (another workload; see the module text)")
-    ap.add_argument("--size", default=None, choices=sorted(HYBRID_SIZES), help="with --design ramupel: one size only")
+    ap.add_argument("--design", default="llama", choices=("llama", "ramupel", "botuvik"),
+                    help="ramupel / botuvik: that design beside the closest others at equal size (another workload; see "
+                         "the module text)")
+    ap.add_argument("--size", default=None, choices=sorted(HYBRID_SIZES), help="with --design ramupel / botuvik: one size only")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -321,7 +376,7 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported by this single-GPU library")
         return 2
-    if args.design == "ramupel":
+    if args.design in ("ramupel", "botuvik"):
         return compare_designs(args, load_peaks())
     args.warmup = max(3, args.warmup)
     repeats = max(1, args.repeats)

@@ -292,7 +292,7 @@ class BotuvikConfig(ArchitectureConfig):
                     hidden_size=d, num_heads=m.heads, num_kv_heads=m.kv_heads, head_dim=m.dim, scale=m.scale,
                     position=position, q=p + "mix.q", k=p + "mix.k", v=p + "mix.v", o=p + "mix.o", value_dim=m.vdim,
                     q_bias=p + "mix.q.b", k_bias=p + "mix.k.b", v_bias=p + "mix.v.b", unit_norm_eps=eps,
-                    softcap=m.softcap, sink=p + "mix.sink")
+                    softcap=m.softcap, sink=p + "mix.sink", exact_weights=True)
             else:
                 mixer = MatrixMemorySpec(
                     hidden_size=d, num_heads=m.heads, key_dim=m.dim, value_dim=m.vdim, norm_eps=eps, gate_cap=m.gate_cap,

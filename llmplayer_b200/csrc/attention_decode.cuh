@@ -162,6 +162,11 @@ __device__ __forceinline__ float sink_term(const ScoreExtras& x, int head, float
     return x.sinks ? exp2f(x.sinks[head] * 1.4426950408889634f - m) : 0.f;
 }
 
+// The softmax weights enter the second product as bfloat16. Where a design wants them applied at float32 precision,
+// a weight e is split into hi = bf16(e) and lo = bf16(e - hi) and the product is formed twice (hi + lo carries 16
+// bits of mantissa, the sums are float32 as before); the row sums always use the float32 weights.
+__device__ __forceinline__ float bf16_rest(float e) { return e - __bfloat162float(__float2bfloat16_rn(e)); }
+
 struct FusedDecodeArgs {
     const float* qkv;          // [B, ld]
     int ld;
@@ -234,7 +239,7 @@ template <bool NAMED, int NT> __device__ __forceinline__ void unit_sync() {
 // each warp awaits its own page at an mbarrier (bounded: `status` is set to 6 if a wait runs out and the page is
 // skipped); else every thread copies 16-byte pieces with cp.async, about 120 instructions per page and thread
 // at a head size of 64, which was most of what the kernel issued. TMA needs hd % 64 == 0 and `smem` aligned to 1024.
-template <int HD_MAX, bool FUSED, int HD_EXACT, bool NAMED, int STAGES, int NW, bool TMA = false, typename Before>
+template <int HD_MAX, bool FUSED, int HD_EXACT, bool NAMED, int STAGES, int NW, bool TMA = false, bool SPLIT = false, typename Before>
 __device__ __forceinline__ void attention_decode_unit(
     uint8_t* smem, const int tid, const int split, const int by, const int b, const __nv_bfloat16* __restrict__ q,
     const __nv_bfloat16* __restrict__ pages, const int* __restrict__ page_table, int pt_stride,
@@ -509,6 +514,11 @@ __device__ __forceinline__ void attention_decode_unit(
                 l1 = l1 * a1 + (e1 + e3);
                 // P^T as the column operand of the second product: (keys 2 t4, 2 t4 + 1 | + 8, head g8)
                 const uint32_t p0 = transpose_8x8(pack_bf16(e0, e1)), p1 = transpose_8x8(pack_bf16(e2, e3));
+                uint32_t r0 = 0, r1 = 0;                 // the rest of the weights beyond their bfloat16 rounding
+                if (SPLIT) {
+                    r0 = transpose_8x8(pack_bf16(bf16_rest(e0), bf16_rest(e1)));
+                    r1 = transpose_8x8(pack_bf16(bf16_rest(e2), bf16_rest(e3)));
+                }
                 const int v_row = key0 + (lane & 7) + (lane >> 4) * 8;          // ldmatrix.x4.trans for V^T, 16 features x 16 keys
                 const int v_chunk = (lane >> 3) & 1;
 #pragma unroll
@@ -518,6 +528,7 @@ __device__ __forceinline__ void attention_decode_unit(
                         uint32_t a[4];
                         ldmatrix_x4_trans(v_tile + tile_offset<TMA>(v_row, mt * 2 + v_chunk, hd, cpr), a[0], a[1], a[2], a[3]);
                         mma_bf16(o[mt], a, p0, p1);
+                        if (SPLIT) mma_bf16(o[mt], a, r0, r1);
                     }
                 }
             }

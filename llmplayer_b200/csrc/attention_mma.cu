@@ -28,7 +28,7 @@ namespace {
 
 // ============================================================================ prefill
 // grid: (tiles of 64 new tokens, H, B); 128 threads.
-template <int HD_MAX>
+template <int HD_MAX, bool SPLIT = false>
 __global__ void __launch_bounds__(128)
 attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
                          const __nv_bfloat16* __restrict__ pages, const int* __restrict__ page_table, int pt_stride,
@@ -122,7 +122,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
             const float a_lo = exp2f(m_lo - mn_lo), a_hi = exp2f(m_hi - mn_hi);
             m_lo = mn_lo; m_hi = mn_hi;
             float sum_lo = 0.f, sum_hi = 0.f;
-            uint32_t pf[4][4];
+            uint32_t pf[4][4], pr[SPLIT ? 4 : 1][4];
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt) {
                 float e0 = s[nt][0] <= NEG_BIG ? 0.f : exp2f(s[nt][0] - mn_lo);
@@ -132,12 +132,19 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
                 sum_lo += e0 + e1; sum_hi += e2 + e3;
                 pf[nt >> 1][(nt & 1) * 2] = pack_bf16(e0, e1);
                 pf[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(e2, e3);
+                if (SPLIT) {
+                    pr[nt >> 1][(nt & 1) * 2] = pack_bf16(bf16_rest(e0), bf16_rest(e1));
+                    pr[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(bf16_rest(e2), bf16_rest(e3));
+                }
             }
             l_lo = l_lo * a_lo + sum_lo; l_hi = l_hi * a_hi + sum_hi;
 #pragma unroll
             for (int i = 0; i < KSTEPS * 2; ++i) { o[i][0] *= a_lo; o[i][1] *= a_lo; o[i][2] *= a_hi; o[i][3] *= a_hi; }
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks) values_16keys<KSTEPS>(o, pf[ks], v_tile, ks * 16, hd, lane);
+            for (int ks = 0; ks < 4; ++ks) {
+                values_16keys<KSTEPS>(o, pf[ks], v_tile, ks * 16, hd, lane);
+                if (SPLIT) values_16keys<KSTEPS>(o, pr[ks], v_tile, ks * 16, hd, lane);
+            }
         }
         __syncthreads();
     }
@@ -165,7 +172,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
 // are computed once, the scale is folded into the exponent's FMA, exp2 is the hardware
 // approximation (relative error 2^-22, far below bfloat16's), and the tiles with the most keys
 // (the last ones of a prompt) are started first.
-template <int HD, int ROWS>
+template <int HD, int ROWS, bool SPLIT = false>
 __global__ void __launch_bounds__(ROWS * 2)
 attention_prefill_exact_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
                                const __nv_bfloat16* __restrict__ pages, const int* __restrict__ page_table,
@@ -288,7 +295,7 @@ attention_prefill_exact_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat1
             const float a_lo = fast_exp2(m_lo - mn_lo), a_hi = fast_exp2(m_hi - mn_hi);
             m_lo = mn_lo; m_hi = mn_hi;
             float sum_lo = 0.f, sum_hi = 0.f;
-            uint32_t pf[4][4];
+            uint32_t pf[4][4], pr[SPLIT ? 4 : 1][4];
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt) {
                 const float e0 = fast_exp2(fmaf(s[nt][0], scale_log2, -mn_lo));      // exp2(-inf) = 0 for masked keys
@@ -298,6 +305,10 @@ attention_prefill_exact_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat1
                 sum_lo += e0 + e1; sum_hi += e2 + e3;
                 pf[nt >> 1][(nt & 1) * 2] = pack_bf16(e0, e1);
                 pf[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(e2, e3);
+                if (SPLIT) {
+                    pr[nt >> 1][(nt & 1) * 2] = pack_bf16(bf16_rest(e0), bf16_rest(e1));
+                    pr[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(bf16_rest(e2), bf16_rest(e3));
+                }
             }
             l_lo = l_lo * a_lo + sum_lo; l_hi = l_hi * a_hi + sum_hi;
 #pragma unroll
@@ -310,6 +321,10 @@ attention_prefill_exact_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat1
                     ldmatrix_x4_trans(v_tile + ks * 16 * ROW + v_off[dd], b0, b1, b2, b3);
                     mma_bf16(o[dd * 2], pf[ks], b0, b1);
                     mma_bf16(o[dd * 2 + 1], pf[ks], b2, b3);
+                    if (SPLIT) {
+                        mma_bf16(o[dd * 2], pr[ks], b0, b1);
+                        mma_bf16(o[dd * 2 + 1], pr[ks], b2, b3);
+                    }
                 }
             }
         }
@@ -339,7 +354,7 @@ attention_prefill_exact_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat1
 // moves lengths on belongs to the end of the previous step, and the step's first kernel is launched without
 // the early start, so it has finished), and the new row is put into the unit's own copy of the page. Every
 // other form waits first (the pages may hold a row that the previous kernel wrote).
-template <int HD_MAX, bool FUSED, int HD_EXACT, int STAGES, int NW = 4>
+template <int HD_MAX, bool FUSED, int HD_EXACT, int STAGES, int NW = 4, bool SPLIT = false>
 __global__ void __launch_bounds__(32 * NW)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pages,
                         const int* __restrict__ page_table, int pt_stride, const int* __restrict__ kv_len,
@@ -350,7 +365,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     lp_grid_release();
     const bool early = FUSED && fused.pages_rw != nullptr;
     if (!early) lp_grid_wait();
-    attention_decode_unit<HD_MAX, FUSED, HD_EXACT, false, STAGES, NW>(
+    attention_decode_unit<HD_MAX, FUSED, HD_EXACT, false, STAGES, NW, false, SPLIT>(
         smem, threadIdx.x, blockIdx.x, blockIdx.y, blockIdx.z, q, pages, page_table, pt_stride, kv_len, part_o, part_ml,
         out, H, G, hd_arg, scale_log2, window, pages_per_split, num_splits, min_share_pages, head_groups, fused,
         [early] { if (early) lp_grid_wait(); });
@@ -445,7 +460,7 @@ static ScoreExtras make_extras(float scale, float softcap, const float* sinks) {
 extern "C" int lp_attention_prefill(const void* q, void* out, const void* pages, const int* page_table, int pt_stride,
                                     const int* q_start, const int* kv_len, int B, int max_new, int H, int G, int hd,
                                     int page_size, float scale, int window, float softcap, const float* sinks,
-                                    cudaStream_t stream) {
+                                    int split_weights, cudaStream_t stream) {
     if (B <= 0 || max_new <= 0) return 0;
     const ScoreExtras extras = make_extras(scale, softcap, sinks);
     int rc = check_geometry("attention_prefill", H, G, hd);
@@ -474,7 +489,33 @@ extern "C" int lp_attention_prefill(const void* q, void* out, const void* pages,
     } while (0)
     // long prompts: 128 query rows share each page of keys; short ones keep 64 rows for more CTAs
     const bool tall = (long long)((max_new + 127) / 128) * H * B >= 8LL * lp_sm_count();
-    if (hd == 64 && tall) LP_PREFILL_EXACT(64, 128);
+    if (split_weights) {
+        // weights applied at float32 precision (hi + lo, see bf16_rest): the same kernels, the second product twice
+#define LP_PREFILL_SPLIT(HDM)                                                                                    \
+    do {                                                                                                         \
+        rc = set_smem(attention_prefill_kernel<HDM, true>, smem, "attention_prefill");                           \
+        if (rc) return rc;                                                                                       \
+        lp_launch(attention_prefill_kernel<HDM, true>, grid, 128, smem, stream,                                  \
+            (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)pages, page_table, pt_stride,     \
+            q_start, kv_len, H, G, hd, scale_log2, window, extras);                                              \
+    } while (0)
+#define LP_PREFILL_EXACT_SPLIT(HD, ROWS)                                                                         \
+    do {                                                                                                         \
+        rc = set_smem(attention_prefill_exact_kernel<HD, ROWS, true>, smem, "attention_prefill");                \
+        if (rc) return rc;                                                                                       \
+        dim3 grid_exact((max_new + ROWS - 1) / ROWS, H, B);                                                      \
+        lp_launch(attention_prefill_exact_kernel<HD, ROWS, true>, grid_exact, ROWS * 2, smem, stream,            \
+                  (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)pages, page_table,         \
+                  pt_stride, q_start, kv_len, H, G, scale_log2, window, extras);                                 \
+    } while (0)
+        if (hd == 64) LP_PREFILL_EXACT_SPLIT(64, 64);
+        else if (hd == 128) LP_PREFILL_EXACT_SPLIT(128, 64);
+        else if (hd <= 64) LP_PREFILL_SPLIT(64); else if (hd <= 96) LP_PREFILL_SPLIT(96); else if (hd <= 128) LP_PREFILL_SPLIT(128);
+        else if (hd <= 192) LP_PREFILL_SPLIT(192); else LP_PREFILL_SPLIT(256);
+#undef LP_PREFILL_EXACT_SPLIT
+#undef LP_PREFILL_SPLIT
+    }
+    else if (hd == 64 && tall) LP_PREFILL_EXACT(64, 128);
     else if (hd == 64) LP_PREFILL_EXACT(64, 64);
     else if (hd == 128 && tall) LP_PREFILL_EXACT(128, 128);
     else if (hd == 128) LP_PREFILL_EXACT(128, 64);
@@ -498,7 +539,7 @@ extern "C" long long lp_attention_decode_scratch(int B, int H, int hd, int num_s
 static int attention_decode_launch(const void* q, void* out, const void* pages, const int* page_table, int pt_stride,
                                    const int* kv_len, float* scratch, int B, int H, int G, int hd, int page_size,
                                    float scale, int window, int pages_per_split, int num_splits, int min_share_pages,
-                                   float softcap, const float* sinks, cudaStream_t stream) {
+                                   float softcap, const float* sinks, int split_weights, cudaStream_t stream) {
     if (B <= 0) return 0;
     FusedDecodeArgs plain_args{};
     plain_args.score = make_extras(scale, softcap, sinks);
@@ -524,8 +565,22 @@ static int attention_decode_launch(const void* q, void* out, const void* pages, 
             (__nv_bfloat16*)out, H, G, hd, scale_log2, window, pages_per_split, num_splits, min_share_pages,     \
             head_groups, plain_args);                                                                            \
     } while (0)
-    if (hd == 64) LP_DECODE(64, 64); else if (hd == 128) LP_DECODE(128, 128);
+#define LP_DECODE_SPLIT(HDM, EXACT)                                                                              \
+    do {                                                                                                         \
+        rc = set_smem(attention_decode_kernel<HDM, false, EXACT, 3, 4, true>, smem, "attention_decode");         \
+        if (rc) return rc;                                                                                       \
+        lp_launch(attention_decode_kernel<HDM, false, EXACT, 3, 4, true>, grid, 128, smem, stream,               \
+            (const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, page_table, pt_stride, kv_len, part_o, part_ml, \
+            (__nv_bfloat16*)out, H, G, hd, scale_log2, window, pages_per_split, num_splits, min_share_pages,     \
+            head_groups, plain_args);                                                                            \
+    } while (0)
+    if (split_weights) {
+        if (hd == 64) LP_DECODE_SPLIT(64, 64); else if (hd == 128) LP_DECODE_SPLIT(128, 128);
+        else if (hd <= 64) LP_DECODE_SPLIT(64, 0); else if (hd <= 128) LP_DECODE_SPLIT(128, 0); else LP_DECODE_SPLIT(256, 0);
+    }
+    else if (hd == 64) LP_DECODE(64, 64); else if (hd == 128) LP_DECODE(128, 128);
     else if (hd <= 64) LP_DECODE(64, 0); else if (hd <= 128) LP_DECODE(128, 0); else LP_DECODE(256, 0);
+#undef LP_DECODE_SPLIT
 #undef LP_DECODE
     rc = lp_check_launch("attention_decode");
     if (rc || num_splits == 1) return rc;
@@ -537,19 +592,19 @@ static int attention_decode_launch(const void* q, void* out, const void* pages, 
 extern "C" int lp_attention_decode(const void* q, void* out, const void* pages, const int* page_table, int pt_stride,
                                    const int* kv_len, float* scratch, int B, int H, int G, int hd, int page_size,
                                    float scale, int window, int pages_per_split, int num_splits, float softcap,
-                                   const float* sinks, cudaStream_t stream) {
+                                   const float* sinks, int split_weights, cudaStream_t stream) {
     return attention_decode_launch(q, out, pages, page_table, pt_stride, kv_len, scratch, B, H, G, hd, page_size, scale,
-                                   window, pages_per_split, num_splits, 0, softcap, sinks, stream);
+                                   window, pages_per_split, num_splits, 0, softcap, sinks, split_weights, stream);
 }
 
 extern "C" int lp_attention_decode_fitted(const void* q, void* out, const void* pages, const int* page_table,
                                           int pt_stride, const int* kv_len, float* scratch, int B, int H, int G, int hd,
                                           int page_size, float scale, int window, int num_splits, int min_share_pages,
-                                          float softcap, const float* sinks, cudaStream_t stream) {
+                                          float softcap, const float* sinks, int split_weights, cudaStream_t stream) {
     if (min_share_pages <= 0) LP_REFUSE("attention_decode_fitted: shares of at least %d pages", min_share_pages);
     return attention_decode_launch(q, out, pages, page_table, pt_stride, kv_len, scratch, B, H, G, hd, page_size, scale,
                                    window, pt_stride > 0 ? pt_stride : 1, num_splits, min_share_pages, softcap, sinks,
-                                   stream);
+                                   split_weights, stream);
 }
 
 // Decode attention that starts from the fused projection output: rotation of queries and of the new key,
@@ -677,5 +732,5 @@ extern "C" int lp_attention_decode_noalloc(const void* q, void* out, const void*
         lp_decode_static_address[device] = address;
     }
     return lp_attention_decode(q, out, pages, page_table, pt_stride, kv_len, lp_decode_static_address[device], B, H, G,
-                               hd, page_size, scale, window, pages_per_split, num_splits, 0.f, nullptr, stream);
+                               hd, page_size, scale, window, pages_per_split, num_splits, 0.f, nullptr, 0, stream);
 }

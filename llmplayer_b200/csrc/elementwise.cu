@@ -628,11 +628,13 @@ __global__ void __launch_bounds__(256)
 qkv_prepare_kernel(const float* __restrict__ qkv, int ld, const float* __restrict__ bias, const float* __restrict__ inv_freq,
                    const int* __restrict__ positions, const int* __restrict__ seq_ids, const int* __restrict__ page_table,
                    int pt_stride, TQ* __restrict__ q_out, TKV* __restrict__ pages, int H, int G, int dk, int dv, int hdp,
-                   int rd, int interleaved, int unit, float unit_eps, int page_size) {
+                   int rd, int interleaved, int unit, float unit_eps, int page_size, float* __restrict__ zero,
+                   long long zero_count) {
     __shared__ float cs[PREP_MAX];
     __shared__ float buf[8][PREP_MAX];
     lp_grid_release();
     lp_grid_wait();
+    clear_on_the_side(zero, zero_count);
     const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int pos = positions[t];
     const int half = rd >> 1;
@@ -688,7 +690,8 @@ qkv_prepare_kernel(const float* __restrict__ qkv, int ld, const float* __restric
 extern "C" int lp_qkv_prepare(const float* qkv, int ld, const float* bias, const float* inv_freq, const int* positions,
                               const int* seq_ids, const int* page_table, int pt_stride, void* q_out, int q_dtype,
                               void* pages, int kv_dtype, int T, int H, int G, int dk, int dv, int hdp, int rd,
-                              int interleaved, int unit, float unit_eps, int page_size, cudaStream_t stream) {
+                              int interleaved, int unit, float unit_eps, int page_size, float* zero, long long zero_count,
+                              cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || G <= 0 || dk <= 0 || dv <= 0) LP_REFUSE("qkv_prepare: %d / %d heads of %d and %d", H, G, dk, dv);
     if (hdp < dk || hdp < dv || dk > PREP_MAX) LP_REFUSE("qkv_prepare: heads of %d and %d stored in %d (at most %d)", dk, dv, hdp, PREP_MAX);
@@ -698,7 +701,8 @@ extern "C" int lp_qkv_prepare(const float* qkv, int ld, const float* bias, const
     if (page_size <= 0 || !pages) LP_REFUSE("qkv_prepare: needs the pages of the cache");
 #define LP_LAUNCH_PREP(TQ, TKV)                                                                                       \
     lp_launch(qkv_prepare_kernel<TQ, TKV>, T, 256, 0, stream, qkv, ld, bias, inv_freq, positions, seq_ids, page_table, \
-              pt_stride, (TQ*)q_out, (TKV*)pages, H, G, dk, dv, hdp, rd, interleaved, unit, unit_eps, page_size)
+              pt_stride, (TQ*)q_out, (TKV*)pages, H, G, dk, dv, hdp, rd, interleaved, unit, unit_eps, page_size, zero,  \
+              zero_count)
     if (q_dtype == LP_F32 && kv_dtype == LP_F32) LP_LAUNCH_PREP(float, float);
     else if (q_dtype == LP_BF16 && kv_dtype == LP_BF16) LP_LAUNCH_PREP(__nv_bfloat16, __nv_bfloat16);
     else LP_REFUSE("qkv_prepare: dtype codes q=%d kv=%d", q_dtype, kv_dtype);
@@ -713,10 +717,12 @@ extern "C" int lp_qkv_prepare(const float* qkv, int ld, const float* bias, const
 template <typename TOut>
 __global__ void __launch_bounds__(NORM_THREADS)
 post_norm_add_kernel(const float* __restrict__ y, const float* __restrict__ w, float eps, float* __restrict__ x,
-                     const float* __restrict__ w2, float eps2, TOut* __restrict__ out2, int d) {
+                     const float* __restrict__ w2, float eps2, TOut* __restrict__ out2, int d, float* __restrict__ zero,
+                     long long zero_count) {
     __shared__ float scratch[32];
     lp_grid_release();
     lp_grid_wait();
+    clear_on_the_side(zero, zero_count);
     const long long row = blockIdx.x;
     const float* yr = y + row * d;
     float* xr = x + row * d;
@@ -737,14 +743,64 @@ post_norm_add_kernel(const float* __restrict__ y, const float* __restrict__ w, f
     for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = lp_from_float<TOut>(xr[i] * f2 * w2[i]);
 }
 
+// The same for rows of a multiple of four values: four values per load and store.
+template <typename TOut>
+__global__ void __launch_bounds__(NORM_THREADS)
+post_norm_add_vec4_kernel(const float* __restrict__ y, const float* __restrict__ w, float eps, float* __restrict__ x,
+                          const float* __restrict__ w2, float eps2, TOut* __restrict__ out2, int d, float* __restrict__ zero,
+                          long long zero_count) {
+    __shared__ float scratch[32];
+    lp_grid_release();
+    lp_grid_wait();
+    clear_on_the_side(zero, zero_count);
+    const long long row = blockIdx.x;
+    const float4* yr = reinterpret_cast<const float4*>(y + row * d);
+    float4* xr = reinterpret_cast<float4*>(x + row * d);
+    const float4* wr = reinterpret_cast<const float4*>(w);
+    const int quads = d >> 2;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < quads; i += blockDim.x) {
+        const float4 v = yr[i];
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = lp_block_sum(ss, scratch);
+    const float f = 1.0f / sqrtf(ss / (float)d + eps);
+    float ss2 = 0.f;
+    for (int i = threadIdx.x; i < quads; i += blockDim.x) {
+        const float4 v = yr[i], g = wr[i];
+        float4 r = xr[i];
+        r.x += v.x * f * g.x; r.y += v.y * f * g.y; r.z += v.z * f * g.z; r.w += v.w * f * g.w;
+        xr[i] = r;
+        ss2 += r.x * r.x + r.y * r.y + r.z * r.z + r.w * r.w;
+    }
+    if (!w2) return;
+    ss2 = lp_block_sum(ss2, scratch);
+    const float f2 = 1.0f / sqrtf(ss2 / (float)d + eps2);
+    const float4* w2r = reinterpret_cast<const float4*>(w2);
+    TOut* o = out2 + row * d;
+    for (int i = threadIdx.x; i < quads; i += blockDim.x) {
+        const float4 r = xr[i], g = w2r[i];
+        store4<TOut>(o + 4 * i, r.x * f2 * g.x, r.y * f2 * g.y, r.z * f2 * g.z, r.w * f2 * g.w);
+    }
+}
+
 extern "C" int lp_post_norm_add(const float* y, const float* w, float eps, float* x, const float* w2, float eps2,
-                                void* out2, int out2_dtype, int T, int d, cudaStream_t stream) {
+                                void* out2, int out2_dtype, int T, int d, float* zero, long long zero_count,
+                                cudaStream_t stream) {
     if (T <= 0 || d <= 0) return 0;
     if (w2 && !out2) LP_REFUSE("post_norm_add: a second norm without its output");
+    if (d % 4 == 0 && (((uintptr_t)y | (uintptr_t)x | (uintptr_t)w | (uintptr_t)w2 | (uintptr_t)out2) & 15) == 0) {
+        if (!w2 || out2_dtype == LP_F32)
+            lp_launch(post_norm_add_vec4_kernel<float>, T, NORM_THREADS, 0, stream, y, w, eps, x, w2, eps2, (float*)out2, d, zero, zero_count);
+        else if (out2_dtype == LP_BF16)
+            lp_launch(post_norm_add_vec4_kernel<__nv_bfloat16>, T, NORM_THREADS, 0, stream, y, w, eps, x, w2, eps2, (__nv_bfloat16*)out2, d, zero, zero_count);
+        else LP_REFUSE("post_norm_add: output dtype code %d", out2_dtype);
+        return lp_check_launch("post_norm_add");
+    }
     if (!w2 || out2_dtype == LP_F32)
-        lp_launch(post_norm_add_kernel<float>, T, NORM_THREADS, 0, stream, y, w, eps, x, w2, eps2, (float*)out2, d);
+        lp_launch(post_norm_add_kernel<float>, T, NORM_THREADS, 0, stream, y, w, eps, x, w2, eps2, (float*)out2, d, zero, zero_count);
     else if (out2_dtype == LP_BF16)
-        lp_launch(post_norm_add_kernel<__nv_bfloat16>, T, NORM_THREADS, 0, stream, y, w, eps, x, w2, eps2, (__nv_bfloat16*)out2, d);
+        lp_launch(post_norm_add_kernel<__nv_bfloat16>, T, NORM_THREADS, 0, stream, y, w, eps, x, w2, eps2, (__nv_bfloat16*)out2, d, zero, zero_count);
     else LP_REFUSE("post_norm_add: output dtype code %d", out2_dtype);
     return lp_check_launch("post_norm_add");
 }
@@ -777,9 +833,11 @@ extern "C" int lp_stream_add(float* x, const float* other, const float* vec, int
 // out[t, f] = max(z[t, f], 0)^2 on the float32 sums of an up projection (z: [T, ldz], may be a slice).
 template <typename TOut>
 __global__ void __launch_bounds__(256)
-relu2_kernel(const float* __restrict__ z, int ldz, TOut* __restrict__ out, int T, int F) {
+relu2_kernel(const float* __restrict__ z, int ldz, TOut* __restrict__ out, int T, int F, float* __restrict__ zero,
+             long long zero_count) {
     lp_grid_release();
     lp_grid_wait();
+    clear_on_the_side(zero, zero_count);
     const long long n = (long long)T * F;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
         const long long t = i / F;
@@ -788,14 +846,43 @@ relu2_kernel(const float* __restrict__ z, int ldz, TOut* __restrict__ out, int T
     }
 }
 
-extern "C" int lp_relu2(const float* z, int ldz, void* out, int out_dtype, int T, int F, cudaStream_t stream) {
+// The same, four values per thread (rows and row starts of a multiple of four values).
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+relu2_vec4_kernel(const float* __restrict__ z, int ldz, TOut* __restrict__ out, int T, int F, float* __restrict__ zero,
+                  long long zero_count) {
+    lp_grid_release();
+    lp_grid_wait();
+    clear_on_the_side(zero, zero_count);
+    const int quads = F >> 2;
+    const long long n = (long long)T * quads;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / quads;
+        const int f = (int)(i - t * quads) * 4;
+        const float4 v = *reinterpret_cast<const float4*>(z + t * ldz + f);
+        const float a = fmaxf(v.x, 0.f), b = fmaxf(v.y, 0.f), c = fmaxf(v.z, 0.f), d = fmaxf(v.w, 0.f);
+        store4<TOut>(out + t * F + f, a * a, b * b, c * c, d * d);
+    }
+}
+
+extern "C" int lp_relu2(const float* z, int ldz, void* out, int out_dtype, int T, int F, float* zero, long long zero_count,
+                        cudaStream_t stream) {
     if (T <= 0 || F <= 0) return 0;
     if (ldz < F) LP_REFUSE("relu2: rows of %d values for %d features", ldz, F);
+    if (F % 4 == 0 && ldz % 4 == 0 && (((uintptr_t)z | (uintptr_t)out) & 15) == 0) {
+        const long long n4 = (long long)T * (F / 4);
+        long long blocks4 = (n4 + 255) / 256;
+        if (blocks4 > 148 * 16) blocks4 = 148 * 16;
+        if (out_dtype == LP_F32) lp_launch(relu2_vec4_kernel<float>, (unsigned)blocks4, 256, 0, stream, z, ldz, (float*)out, T, F, zero, zero_count);
+        else if (out_dtype == LP_BF16) lp_launch(relu2_vec4_kernel<__nv_bfloat16>, (unsigned)blocks4, 256, 0, stream, z, ldz, (__nv_bfloat16*)out, T, F, zero, zero_count);
+        else LP_REFUSE("relu2: output dtype code %d", out_dtype);
+        return lp_check_launch("relu2");
+    }
     const long long n = (long long)T * F;
     long long blocks = (n + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
-    if (out_dtype == LP_F32) lp_launch(relu2_kernel<float>, (unsigned)blocks, 256, 0, stream, z, ldz, (float*)out, T, F);
-    else if (out_dtype == LP_BF16) lp_launch(relu2_kernel<__nv_bfloat16>, (unsigned)blocks, 256, 0, stream, z, ldz, (__nv_bfloat16*)out, T, F);
+    if (out_dtype == LP_F32) lp_launch(relu2_kernel<float>, (unsigned)blocks, 256, 0, stream, z, ldz, (float*)out, T, F, zero, zero_count);
+    else if (out_dtype == LP_BF16) lp_launch(relu2_kernel<__nv_bfloat16>, (unsigned)blocks, 256, 0, stream, z, ldz, (__nv_bfloat16*)out, T, F, zero, zero_count);
     else LP_REFUSE("relu2: output dtype code %d", out_dtype);
     return lp_check_launch("relu2");
 }

@@ -193,8 +193,7 @@ gla_combine_kernel(float* __restrict__ state, const int* __restrict__ slots, con
 //     m_t = max(f + m_(t-1), i)                             the running maximum (the sequence's m starts at 0)
 //     decay[t] = exp(f + m_(t-1) - m_t),  gain[t] = exp(i - m_t),  max_row[t] = m_t
 // so that S_t = decay S_(t-1) + gain k v^T is the recurrence in a stabilised form (matrix memory of the xLSTM family).
-// One block per sequence: all threads form i and f of its new tokens, then one thread per head walks them in order.
-// m is kept per slot and head in `mstate`.
+// One block per sequence and head walks the sequence's new tokens 256 at a time. m is kept per slot and head in `mstate`.
 __device__ __forceinline__ float lp_log_sigmoid(float v) { return -(fmaxf(-v, 0.f) + log1pf(expf(-fabsf(v)))); }
 
 __global__ void __launch_bounds__(256)
@@ -202,35 +201,59 @@ exp_gates_kernel(const float* __restrict__ proj, int ld, int i_off, int f_off, c
                  const float* __restrict__ bias_f, float cap, float* __restrict__ mstate, const int* __restrict__ slots,
                  const int* __restrict__ q_start, float* __restrict__ decay, float* __restrict__ gain,
                  float* __restrict__ max_row, int H) {
+    __shared__ float warp_f[8], warp_i[8];
+    __shared__ float ms[257];
     lp_grid_release();
     lp_grid_wait();
-    const int b = blockIdx.x;
+    const int b = blockIdx.x, h = blockIdx.y;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int t0 = q_start[b], t1 = q_start[b + 1];
-    const int n = (t1 - t0) * H;
-    for (int e = threadIdx.x; e < n; e += blockDim.x) {
-        const int t = t0 + e / H, h = e % H;
-        const float zi = proj[(long long)t * ld + i_off + h] + (bias_i ? bias_i[h] : 0.f);
-        const float zf = proj[(long long)t * ld + f_off + h] + (bias_f ? bias_f[h] : 0.f);
-        const float li = cap > 0.f ? cap * tanhf(zi / cap) : zi;
-        const float lf = lp_log_sigmoid(cap > 0.f ? cap * tanhf(zf / cap) : zf);
-        gain[(long long)t * H + h] = li;
-        decay[(long long)t * H + h] = lf;
-    }
-    __syncthreads();
-    for (int h = threadIdx.x; h < H; h += blockDim.x) {
-        float* ms = mstate + (long long)slots[b] * H + h;
-        float m = *ms;
-        for (int t = t0; t < t1; ++t) {
-            const long long at = (long long)t * H + h;
-            const float li = gain[at], lf = decay[at];
-            const float mn = fmaxf(lf + m, li);
-            decay[at] = expf(lf + m - mn);
-            gain[at] = expf(li - mn);
-            max_row[at] = mn;
-            m = mn;
+    float* mp = mstate + (long long)slots[b] * H + h;
+    float carry = *mp;
+    const float bi = bias_i ? bias_i[h] : 0.f, bf = bias_f ? bias_f[h] : 0.f;
+    // A token is the map m -> max(m + f, i); maps compose as (f1, i1) then (f2, i2) = (f1 + f2, max(i1 + f2, i2)), so
+    // the maxima of 256 tokens at a time come from a scan over the block: within warps by shuffles, then over the warps.
+    for (int base = t0; base < t1; base += 256) {
+        const int t = base + tid;
+        const bool valid = t < t1;
+        float li = 0.f, lf = 0.f, F = 0.f, I = -INFINITY;          // the identity map for threads beyond the end
+        if (valid) {
+            const float zi = proj[(long long)t * ld + i_off + h] + bi;
+            const float zf = proj[(long long)t * ld + f_off + h] + bf;
+            li = cap > 0.f ? cap * tanhf(zi / cap) : zi;
+            lf = lp_log_sigmoid(cap > 0.f ? cap * tanhf(zf / cap) : zf);
+            F = lf;
+            I = li;
         }
-        *ms = m;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float pf = __shfl_up_sync(0xffffffffu, F, o), pi = __shfl_up_sync(0xffffffffu, I, o);
+            if (lane >= o) {
+                I = fmaxf(pi + F, I);
+                F = pf + F;
+            }
+        }
+        if (lane == 31) { warp_f[warp] = F; warp_i[warp] = I; }
+        __syncthreads();
+        float af = 0.f, ai = -INFINITY;                            // the warps in front of this one
+        for (int w = 0; w < warp; ++w) {
+            ai = fmaxf(ai + warp_f[w], warp_i[w]);
+            af += warp_f[w];
+        }
+        const float m = fmaxf(carry + (af + F), fmaxf(ai + F, I));
+        ms[tid + 1] = m;
+        if (tid == 0) ms[0] = carry;
+        __syncthreads();
+        if (valid) {
+            const long long at = (long long)t * H + h;
+            decay[at] = expf(lf + ms[tid] - m);
+            gain[at] = expf(li - m);
+            max_row[at] = m;
+        }
+        carry = ms[min(256, t1 - base)];
+        __syncthreads();
     }
+    if (tid == 0) *mp = carry;
 }
 
 // ---------------------------------------------------------------- finish
@@ -366,7 +389,8 @@ extern "C" int lp_exp_gates(const float* proj, int ld, int i_off, int f_off, con
     if (B <= 0) return 0;
     if (H <= 0 || i_off < 0 || f_off < 0 || i_off + H > ld || f_off + H > ld)
         LP_REFUSE("exp_gates: %d heads at %d and %d in rows of %d", H, i_off, f_off, ld);
-    lp_launch(exp_gates_kernel, B, 256, 0, stream, proj, ld, i_off, f_off, bias_i, bias_f, cap, mstate, slots, q_start,
+    if (H > 65535) LP_REFUSE("exp_gates: %d heads exceed the grid", H);
+    lp_launch(exp_gates_kernel, dim3(B, H), 256, 0, stream, proj, ld, i_off, f_off, bias_i, bias_f, cap, mstate, slots, q_start,
               decay, gain, max_row, H);
     return lp_check_launch("exp_gates");
 }

@@ -103,6 +103,8 @@ class Model:
                                    self._vectors[run.add_vector][run.add_row] if run.add_vector is not None else None)
                 ready = False
             following = self.blocks[self.runs[i + 1].layer] if i + 1 < len(self.runs) else None
+            if following is not None and (self.runs[i + 1].add_embedding or self.runs[i + 1].add_vector is not None):
+                following = None         # something is added to the stream before that run: its norm cannot be written yet
             if self._chains[run.layer]:
                 ready = bool(block.forward(ctx, cache.view(self.cache_owner(i)), x, normed_ready=ready,
                                            next_block=following))

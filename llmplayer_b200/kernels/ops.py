@@ -31,14 +31,15 @@ _SIGNATURES = {
         "lp_rope_cache_write": [_P, _I, _P, _P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
         "lp_advance": [_P, _P, _P, _P, _I, _P],
         "lp_rope_angles": [_P, _P, _P, _I, _I, _P],
-        "lp_qkv_prepare": [_P, _I, _P, _P, _P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
-        "lp_post_norm_add": [_P, _P, _F, _P, _P, _F, _P, _I, _I, _I, _P],
+        "lp_qkv_prepare": [_P, _I, _P, _P, _P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P,
+                           ctypes.c_longlong, _P],
+        "lp_post_norm_add": [_P, _P, _F, _P, _P, _F, _P, _I, _I, _I, _P, ctypes.c_longlong, _P],
         "lp_stream_add": [_P, _P, _P, _I, _I, _P],
-        "lp_relu2": [_P, _I, _P, _I, _I, _I, _P],
+        "lp_relu2": [_P, _I, _P, _I, _I, _I, _P, ctypes.c_longlong, _P],
     },
     "routing": {
         "lp_route": [_P, _I, _P, _I, _I, _I, _I, _I, _I, _P],
-        "lp_expert_scale": [_P, _I, _I, _P, _I, _I, _I, _I, _P],
+        "lp_expert_scale": [_P, _I, _I, _P, _I, _I, _I, _I, _P, ctypes.c_longlong, _P],
     },
     "gemm_plain": {
         "lp_gemm_plain": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
@@ -55,9 +56,9 @@ _SIGNATURES = {
         "lp_gemm_qkv_rope": [_P, _P, _I, _I, _I, _I, _P, _I, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _P, _P],
     },
     "attention_mma": {
-        "lp_attention_prefill": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _F, _P, _P],
-        "lp_attention_decode": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _P],
-        "lp_attention_decode_fitted": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _P],
+        "lp_attention_prefill": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _F, _P, _I, _P],
+        "lp_attention_decode": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _I, _P],
+        "lp_attention_decode_fitted": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _I, _P],
         "lp_attention_decode_fused": [_P, _I, _P, _I, _I, _P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I,
                                       _I, _I, _I, _P, _F, _I, ctypes.c_longlong, _P, _P],
     },
@@ -880,9 +881,12 @@ tcgen05_attention = True      # tests switch it off to reach the mma.sync kernel
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, page_table: torch.Tensor,
                       q_start: torch.Tensor, kv_len: torch.Tensor, max_new: int, *, num_heads: int,
                       num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
-                      softcap: Optional[float] = None, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      softcap: Optional[float] = None, sinks: Optional[torch.Tensor] = None,
+                      exact_weights: bool = False) -> torch.Tensor:
     """Tensor-core attention for a step that brings several tokens per sequence.
-    ``q_start`` [B+1]: offsets of each sequence's new tokens; ``kv_len`` [B]: lengths after the step."""
+    ``q_start`` [B+1]: offsets of each sequence's new tokens; ``kv_len`` [B]: lengths after the step.
+    ``exact_weights``: the softmax weights enter the product with the values at float32 precision (as a bfloat16
+    value plus a bfloat16 rest, two products) instead of rounded to bfloat16."""
     _check_attention(q, out, pages, page_table, num_heads, num_kv_heads, head_dim, "attention_prefill")
     _want(q_start, "attention_prefill q_start", torch.int32, 1)
     _want(kv_len, "attention_prefill kv_len", torch.int32, 1)
@@ -890,7 +894,7 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, p
     if q_start.numel() != B + 1 or page_table.shape[0] != B:
         raise KernelError(f"attention_prefill: {B} sequences, {q_start.numel()} offsets, table {tuple(page_table.shape)}")
     _check_sinks(sinks, num_heads, "attention_prefill")
-    if head_dim in (64, 128) and max_new > 64 and tcgen05_attention and not softcap and sinks is None:
+    if head_dim in (64, 128) and max_new > 64 and tcgen05_attention and not softcap and sinks is None and not exact_weights:
         # long runs of new tokens with heads of 64 or 128: scores and P V on the tcgen05 tensor cores
         lib = library("attention_tcgen05")
         _check(lib, lib.lp_attention_prefill_tc(
@@ -903,7 +907,7 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, p
     _check(lib, lib.lp_attention_prefill(
         q.data_ptr(), out.data_ptr(), pages.data_ptr(), page_table.data_ptr(), page_table.shape[1],
         q_start.data_ptr(), kv_len.data_ptr(), B, int(max_new), num_heads, num_kv_heads, head_dim, pages.shape[3],
-        float(scale), int(window) if window else 0, float(softcap or 0.0), _ptr(sinks), _stream()))
+        float(scale), int(window) if window else 0, float(softcap or 0.0), _ptr(sinks), 1 if exact_weights else 0, _stream()))
     return out
 
 
@@ -932,7 +936,8 @@ def decode_split(batch: int, num_kv_heads: int, num_heads: int, table_width: int
 def attention_decode(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, page_table: torch.Tensor,
                      kv_len: torch.Tensor, scratch, *, num_heads: int, num_kv_heads: int, head_dim: int,
                      scale: float, window: Optional[int], pages_per_split: int = 0, num_splits: int = 0,
-                     softcap: Optional[float] = None, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     softcap: Optional[float] = None, sinks: Optional[torch.Tensor] = None,
+                     exact_weights: bool = False) -> torch.Tensor:
     """Tensor-core attention for a step of one token per sequence. ``scratch(name, shape, dtype)``
     supplies the float32 buffer for the partial results of the shares."""
     _check_attention(q, out, pages, page_table, num_heads, num_kv_heads, head_dim, "attention_decode")
@@ -950,12 +955,14 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, pa
         _check(lib, lib.lp_attention_decode_fitted(
             q.data_ptr(), out.data_ptr(), pages.data_ptr(), page_table.data_ptr(), page_table.shape[1],
             kv_len.data_ptr(), buf.data_ptr(), B, num_heads, num_kv_heads, head_dim, pages.shape[3], float(scale),
-            int(window) if window else 0, num_splits, MIN_SHARE_PAGES, float(softcap or 0.0), _ptr(sinks), _stream()))
+            int(window) if window else 0, num_splits, MIN_SHARE_PAGES, float(softcap or 0.0), _ptr(sinks),
+            1 if exact_weights else 0, _stream()))
         return out
     _check(lib, lib.lp_attention_decode(
         q.data_ptr(), out.data_ptr(), pages.data_ptr(), page_table.data_ptr(), page_table.shape[1], kv_len.data_ptr(),
         buf.data_ptr(), B, num_heads, num_kv_heads, head_dim, pages.shape[3], float(scale),
-        int(window) if window else 0, pages_per_split, num_splits, float(softcap or 0.0), _ptr(sinks), _stream()))
+        int(window) if window else 0, pages_per_split, num_splits, float(softcap or 0.0), _ptr(sinks),
+        1 if exact_weights else 0, _stream()))
     return out
 
 
@@ -1016,18 +1023,19 @@ def attention_decode_fused(qkv: torch.Tensor, rotation: Rotation, out: torch.Ten
 
 def attention(ctx, q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, page_table: torch.Tensor, *,
               num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
-              fast: bool, softcap: Optional[float] = None, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
+              fast: bool, softcap: Optional[float] = None, sinks: Optional[torch.Tensor] = None,
+              exact_weights: bool = False) -> torch.Tensor:
     """Attention of the step's tokens over the cache; picks the kernel for the step's shape."""
     tensor_cores = (fast and q.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16
                     and head_dim % 16 == 0 and head_dim <= 256)
     if tensor_cores and ctx.all_single:
         return attention_decode(q, out, pages, page_table, ctx.kv_len, ctx.buffer, num_heads=num_heads,
                                 num_kv_heads=num_kv_heads, head_dim=head_dim, scale=scale, window=window,
-                                softcap=softcap, sinks=sinks)
+                                softcap=softcap, sinks=sinks, exact_weights=exact_weights)
     if tensor_cores:
         return attention_prefill(q, out, pages, page_table, ctx.q_start, ctx.kv_len, ctx.max_new,
                                  num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim, scale=scale,
-                                 window=window, softcap=softcap, sinks=sinks)
+                                 window=window, softcap=softcap, sinks=sinks, exact_weights=exact_weights)
     return attention_plain(q, out, pages, page_table, ctx.seq_ids, ctx.positions, num_heads=num_heads,
                            num_kv_heads=num_kv_heads, head_dim=head_dim, scale=scale, window=window, softcap=softcap,
                            sinks=sinks)
@@ -1349,7 +1357,8 @@ def exp_gates(proj: torch.Tensor, i_off: int, f_off: int, bias_i: Optional[torch
 # --------------------------------------------------------------------------- general attention heads, sublayer norms
 def qkv_prepare(qkv: torch.Tensor, bias: Optional[torch.Tensor], rotation: Rotation, positions: torch.Tensor,
                 seq_ids: torch.Tensor, page_table: torch.Tensor, q_out: torch.Tensor, pages: torch.Tensor, *,
-                num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, unit_norm_eps: Optional[float]) -> None:
+                num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, unit_norm_eps: Optional[float],
+                clear: Optional[torch.Tensor] = None) -> None:
     """From the float32 projection ``qkv`` [T, H * dk + G * dk + G * dv]: add ``bias`` (float32, same width, or None),
     rotate queries and keys, divide each query and key head by its root mean square (``unit_norm_eps`` not None), and
     store queries to ``q_out`` [T, H * hdp] and keys and values into ``pages`` [num_pages, 2, G, page_size, hdp], every
@@ -1376,11 +1385,12 @@ def qkv_prepare(qkv: torch.Tensor, bias: Optional[torch.Tensor], rotation: Rotat
         qkv.data_ptr(), qkv.shape[1], _ptr(bias), freq_ptr, positions.data_ptr(), seq_ids.data_ptr(),
         page_table.data_ptr(), page_table.shape[1], q_out.data_ptr(), _code(q_out, "qkv_prepare q_out"), pages.data_ptr(),
         _code(pages, "qkv_prepare pages"), T, H, G, dk, dv, hdp, rotary_dim, interleaved,
-        0 if unit_norm_eps is None else 1, float(unit_norm_eps or 0.0), pages.shape[3], _stream()))
+        0 if unit_norm_eps is None else 1, float(unit_norm_eps or 0.0), pages.shape[3], *_clear_args(clear, "qkv_prepare"),
+        _stream()))
 
 
 def post_norm_add(y: torch.Tensor, weight: torch.Tensor, eps: float, x: torch.Tensor, *, next_weight: Optional[torch.Tensor] = None,
-                  next_eps: float = 0.0, next_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                  next_eps: float = 0.0, next_out: Optional[torch.Tensor] = None, clear: Optional[torch.Tensor] = None) -> torch.Tensor:
     """x += y / sqrt(mean(y^2) + eps) * weight, float32 in place; with ``next_weight``, also
     next_out = x / sqrt(mean(x^2) + next_eps) * next_weight of the new x (the norm in front of the next sublayer)."""
     _want(y, "post_norm_add y", torch.float32, 2)
@@ -1399,7 +1409,7 @@ def post_norm_add(y: torch.Tensor, weight: torch.Tensor, eps: float, x: torch.Te
     lib = library("elementwise")
     _check(lib, lib.lp_post_norm_add(y.data_ptr(), weight.data_ptr(), float(eps), x.data_ptr(), _ptr(next_weight),
                                      float(next_eps), _ptr(next_out) if next_weight is not None else None, code, T, d,
-                                     _stream()))
+                                     *_clear_args(clear, "post_norm_add"), _stream()))
     return x
 
 
@@ -1420,14 +1430,15 @@ def stream_add(x: torch.Tensor, other: Optional[torch.Tensor] = None, vector: Op
     return x
 
 
-def relu2(z: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+def relu2(z: torch.Tensor, out: torch.Tensor, clear: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out = max(z, 0)^2; ``z``: float32 [T, F] (may be a column slice)."""
     zp, ldz = _slice(z, "relu2 z")
     _want(out, "relu2 out", ndim=2)
     if out.shape != z.shape:
         raise KernelError(f"relu2: z {tuple(z.shape)}, out {tuple(out.shape)}")
     lib = library("elementwise")
-    _check(lib, lib.lp_relu2(zp, ldz, out.data_ptr(), _code(out, "relu2 out"), z.shape[0], z.shape[1], _stream()))
+    _check(lib, lib.lp_relu2(zp, ldz, out.data_ptr(), _code(out, "relu2 out"), z.shape[0], z.shape[1],
+                             *_clear_args(clear, "relu2"), _stream()))
     return out
 
 
@@ -1447,7 +1458,7 @@ def route(logits: torch.Tensor, weights: torch.Tensor, *, groups: int, keep: int
     return weights
 
 
-def expert_scale(hidden: torch.Tensor, weights: torch.Tensor, expert_size: int) -> torch.Tensor:
+def expert_scale(hidden: torch.Tensor, weights: torch.Tensor, expert_size: int, clear: Optional[torch.Tensor] = None) -> torch.Tensor:
     """hidden[t, e * expert_size + j] *= weights[t, e] in place for the E experts of ``weights`` [T, E]; columns of
     ``hidden`` beyond E * expert_size are left as they are."""
     _want(hidden, "expert_scale hidden", ndim=2)
@@ -1457,7 +1468,7 @@ def expert_scale(hidden: torch.Tensor, weights: torch.Tensor, expert_size: int) 
         raise KernelError(f"expert_scale: hidden {tuple(hidden.shape)} for {E} experts of {expert_size}")
     lib = library("routing")
     _check(lib, lib.lp_expert_scale(hidden.data_ptr(), _code(hidden, "expert_scale hidden"), hidden.shape[1],
-                                    weights.data_ptr(), E, T, E, int(expert_size), _stream()))
+                                    weights.data_ptr(), E, T, E, int(expert_size), *_clear_args(clear, "expert_scale"), _stream()))
     return hidden
 
 

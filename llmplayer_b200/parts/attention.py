@@ -128,7 +128,7 @@ class Attention(Part):
         with ops.section("attention.out"):
             self.out.few(o, residual, ops.ACCUMULATE, zero=sums[:ops.FEW_TOKENS + T * F])
 
-    def _forward_general(self, ctx, cache, x, residual: torch.Tensor, then_norm=None) -> bool:
+    def _forward_general(self, ctx, cache, x, residual: torch.Tensor, then_norm=None, overwrite: bool = False) -> bool:
         """A layer with biases, unit-norm heads, capped scores, sinks or values of another size than its keys:
         projection with float32 sums, one kernel that adds the biases, rotates, norms and stores queries, keys and
         values (heads padded to ``stored_dim``), then the attention kernels with the cap and the sinks as arguments."""
@@ -146,23 +146,33 @@ class Attention(Part):
             self.qkv.store(x, qkv, ctx)
         q = ctx.buffer("q", (T, H * hd), rt.act_dtype)
         with ops.section("attention.position"):
+            # an output product that sums partial results wants its target zero: this kernel clears it on the side
+            clear = residual if overwrite and residual.dtype == torch.float32 and self.out.needs_zero(T) else None
             ops.qkv_prepare(qkv, self.bias, rotation, ctx.positions, ctx.seq_ids, table, q, cache.pages, num_heads=H,
-                            num_kv_heads=G, key_dim=s.head_dim, value_dim=self.value_dim, unit_norm_eps=s.unit_norm_eps)
+                            num_kv_heads=G, key_dim=s.head_dim, value_dim=self.value_dim, unit_norm_eps=s.unit_norm_eps,
+                            clear=clear)
         o = ctx.buffer("attn_out", (T, H * hd), rt.act_dtype)
         with ops.section("attention.scores"):
             ops.attention(ctx, q, o, cache.pages, table, num_heads=H, num_kv_heads=G, head_dim=hd, scale=s.scale,
-                          window=s.window, fast=rt.fast, softcap=s.softcap, sinks=self.sinks)
+                          window=s.window, fast=rt.fast, softcap=s.softcap, sinks=self.sinks, exact_weights=s.exact_weights)
         with ops.section("attention.out"):
+            if overwrite:
+                if clear is not None:
+                    ctx.note_cleared()
+                self.out.store(o, residual, ctx)
+                return False
             return self.out.accumulate(o, residual, ctx, then_norm)
 
-    def forward(self, ctx, cache, x, residual: torch.Tensor, then_norm=None) -> bool:
-        """Adds the layer's output into ``residual``; returns whether ``then_norm`` was fused.
-        ``x``: the normed stream, or a :class:`PendingNorm` of it."""
+    def forward(self, ctx, cache, x, residual: torch.Tensor, then_norm=None, overwrite: bool = False) -> bool:
+        """Adds the layer's output into ``residual`` (``overwrite``: stores it there instead); returns whether
+        ``then_norm`` was fused. ``x``: the normed stream, or a :class:`PendingNorm` of it."""
         s, rt = self.spec, self.runtime
         if cache is None:
             raise ConfigError("attention needs a key/value cache (its own or another run's)")
         if s.general:
-            return self._forward_general(ctx, cache, x, residual, then_norm)
+            return self._forward_general(ctx, cache, x, residual, then_norm, overwrite)
+        if overwrite:
+            residual.zero_()
         H, G, hd = s.num_heads, s.num_kv_heads, s.head_dim
         # the position encoding as something the kernels do on the way (a rotation), or None: then the
         # encoding's own part changes queries and keys in the projection's output before the kernels run

@@ -242,7 +242,7 @@ class ParallelBlock(Part):
 
 class SandwichBlock(Part):
     """x += post_norm(mixer(norm(x))); x += post_norm(ffn(norm(x))): a norm in front of and behind each sublayer.
-    A sublayer adds its result into a zeroed float32 buffer; one kernel then norms that result, adds it into the
+    A sublayer stores its result in a float32 buffer (or adds it into the zeroed buffer, if it can only add); one kernel then norms that result, adds it into the
     stream and, when a further sublayer of this layer follows, writes that sublayer's input norm in the same pass.
     The norms are RMS norms (the kernel's rule); the feed-forward may be absent."""
 
@@ -259,6 +259,9 @@ class SandwichBlock(Part):
         for norm in (self.mixer_norm, self.post_mixer_norm, self.ffn_norm, self.post_ffn_norm):
             if norm is not None and not getattr(norm, "fusable_rms", False):
                 raise ConfigError("the norms of a sandwich block are RMS norms")
+        # a part whose forward takes `overwrite` stores its result; any other adds it into a buffer zeroed first
+        self._mixer_stores = "overwrite" in inspect.signature(self.mixer.forward).parameters
+        self._ffn_stores = self.ffn is not None and "overwrite" in inspect.signature(self.ffn.forward).parameters
 
     def children(self):
         return tuple(p for p in (self.mixer_norm, self.mixer, self.post_mixer_norm, self.ffn_norm, self.ffn,
@@ -282,28 +285,48 @@ class SandwichBlock(Part):
     def cache_request(self):
         return self.mixer.cache_request()
 
-    def forward(self, ctx, cache, residual: torch.Tensor) -> bool:
+    kind_sandwich = True
+
+    def forward(self, ctx, cache, residual: torch.Tensor, normed_ready: bool = False, next_block=None) -> bool:
+        """Run the layer on the residual stream in place. ``normed_ready``: the previous block already left this
+        block's first norm of the stream in the shared "normed" buffer. ``next_block``: the block that runs next on
+        the stream as this one leaves it; if it is of this kind, the kernel that adds this layer's last result also
+        writes that block's first norm. Returns whether it did. A norm kernel also clears, on the side, the buffer
+        that the product after it sums partial results into (``buffer_to_clear`` of the part that follows)."""
         act = self.runtime.act_dtype
+        T = residual.shape[0]
         h = ctx.buffer("normed", tuple(residual.shape), act)
         y = ctx.buffer("sublayer_out", tuple(residual.shape), torch.float32)
-        with ops.section("norm"):
-            self.mixer_norm.apply(residual, h)
+        if not normed_ready:
+            PreNormBlock._norm(ctx, self.mixer_norm, self.mixer, residual, h)
+        if self._mixer_stores:
+            self.mixer.forward(ctx, cache, h, y, overwrite=True)
+        else:
             y.zero_()
-        self.mixer.forward(ctx, cache, h, y)
-        post = self.post_mixer_norm
-        with ops.section("norm"):
-            if self.ffn is None:
-                ops.post_norm_add(y, post.weight, post.spec.eps, residual)
-                return False
-            nxt = self.ffn_norm
-            ops.post_norm_add(y, post.weight, post.spec.eps, residual, next_weight=nxt.weight, next_eps=nxt.spec.eps,
-                              next_out=h)
+            self.mixer.forward(ctx, cache, h, y)
+        follower = next_block if getattr(next_block, "kind_sandwich", False) else None
+
+        def add_normed(post, next_norm, consumer) -> bool:
+            with ops.section("norm"):
+                if next_norm is None:
+                    ops.post_norm_add(y, post.weight, post.spec.eps, residual)
+                    return False
+                clear = PreNormBlock._clear_for(ctx, consumer, T)
+                ops.post_norm_add(y, post.weight, post.spec.eps, residual, next_weight=next_norm.weight,
+                                  next_eps=next_norm.spec.eps, next_out=h, clear=clear)
+                if clear is not None:
+                    ctx.note_cleared()
+                return True
+
+        if self.ffn is None:
+            return add_normed(self.post_mixer_norm, follower.mixer_norm if follower else None, follower.mixer if follower else None)
+        add_normed(self.post_mixer_norm, self.ffn_norm, self.ffn)
+        if self._ffn_stores:
+            self.ffn.forward(ctx, h, y, overwrite=True)
+        else:
             y.zero_()
-        self.ffn.forward(ctx, h, y)
-        post = self.post_ffn_norm
-        with ops.section("norm"):
-            ops.post_norm_add(y, post.weight, post.spec.eps, residual)
-        return False
+            self.ffn.forward(ctx, h, y)
+        return add_normed(self.post_ffn_norm, follower.mixer_norm if follower else None, follower.mixer if follower else None)
 
 
 BLOCKS.register("sandwich", SandwichBlock)

@@ -159,7 +159,12 @@ class SquaredReLU(Part):
         self.up = Linear([tensors[self.spec.up]], runtime)
         self.down = Linear([tensors[self.spec.down]], runtime)
 
-    def forward(self, ctx, x, residual: torch.Tensor) -> bool:
+    def buffer_to_clear(self, ctx, tokens: int):
+        from ..kernels import ops
+        return self.up.sums_into(ctx, tokens, "ffn_up", ops.STORE)
+
+    def forward(self, ctx, x, residual: torch.Tensor, overwrite: bool = False) -> bool:
+        """Adds the feed-forward's output into ``residual`` (``overwrite``: stores it there instead)."""
         from ..kernels import ops
         if isinstance(x, PendingNorm):
             x = x.tensor()
@@ -169,9 +174,15 @@ class SquaredReLU(Part):
             self.up.store(x, z, ctx)
         h = ctx.buffer("ffn_hidden", (T, F), self.runtime.act_dtype)
         with ops.section("ffn.act"):
-            ops.relu2(z, h)
+            clear = residual if overwrite and residual.dtype == torch.float32 and self.down.needs_zero(T) else None
+            ops.relu2(z, h, clear=clear)
         with ops.section("ffn.down"):
-            self.down.accumulate(h, residual, ctx)
+            if clear is not None:
+                ctx.note_cleared()
+            if overwrite:
+                self.down.store(h, residual, ctx)
+            else:
+                self.down.accumulate(h, residual, ctx)
         return False
 
 
@@ -232,7 +243,12 @@ class Mixture(Part):
         self.gate_up = Linear([gate, up], runtime, gated=True)
         self.down = Linear([down], runtime)
 
-    def forward(self, ctx, x, residual: torch.Tensor) -> bool:
+    def buffer_to_clear(self, ctx, tokens: int):
+        from ..kernels import ops
+        return self.router.sums_into(ctx, tokens, "router_logits", ops.STORE)
+
+    def forward(self, ctx, x, residual: torch.Tensor, overwrite: bool = False) -> bool:
+        """Adds the mixture's output into ``residual`` (``overwrite``: stores it there instead)."""
         from ..kernels import ops
         s, r = self.spec, self.spec.routing
         if isinstance(x, PendingNorm):
@@ -247,9 +263,15 @@ class Mixture(Part):
         with ops.section("ffn.gate_up"):
             self.gate_up.swiglu(x, h, ctx)
         with ops.section("ffn.weights"):
-            ops.expert_scale(h, weights, s.expert_size)
+            clear = residual if overwrite and residual.dtype == torch.float32 and self.down.needs_zero(T) else None
+            ops.expert_scale(h, weights, s.expert_size, clear=clear)
         with ops.section("ffn.down"):
-            self.down.accumulate(h, residual, ctx)
+            if clear is not None:
+                ctx.note_cleared()
+            if overwrite:
+                self.down.store(h, residual, ctx)
+            else:
+                self.down.accumulate(h, residual, ctx)
         return False
 
 

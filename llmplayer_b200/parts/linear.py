@@ -80,6 +80,13 @@ class Linear:
             return None
         return ctx.buffer(out_name, (tokens, self.out_features), torch.float32)
 
+    def needs_zero(self, tokens: int, mode: int = ops.STORE) -> bool:
+        """Whether this product, run for ``tokens`` rows in ``mode``, adds partial sums into its output, which must
+        therefore be zero beforehand (a kernel in front may clear it on the side and say so with ``ctx.note_cleared()``)."""
+        if not self._fast() or mode != ops.STORE:
+            return False
+        return ops.gemm_plan(tokens, self.out_features, self.in_features, mode)[1] > 1
+
     def can_few(self, tokens: int, mode: int) -> bool:
         """Whether :meth:`few` serves this product for ``tokens`` rows."""
         return self._fast() and tokens <= ops.FEW_TOKENS and (mode != ops.SWIGLU or self.interleaved)

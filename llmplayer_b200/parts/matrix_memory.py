@@ -77,8 +77,11 @@ class MatrixMemory(Part):
                 StateRequest((s.num_heads,), torch.float32))
 
     # ------------------------------------------------------------------ step
-    def forward(self, ctx, cache, x, residual: torch.Tensor) -> bool:
-        """Adds the mixer's output into ``residual``."""
+    def buffer_to_clear(self, ctx, tokens: int):
+        return self.proj.sums_into(ctx, tokens, "mixer_proj", ops.STORE)
+
+    def forward(self, ctx, cache, x, residual: torch.Tensor, overwrite: bool = False) -> bool:
+        """Adds the mixer's output into ``residual`` (``overwrite``: stores it there instead)."""
         s, rt = self.spec, self.runtime
         if cache is None:
             raise ConfigError("a matrix memory needs its per-sequence state")
@@ -105,10 +108,17 @@ class MatrixMemory(Part):
                          decay_per_head=True, key_gain=gates[1], ones_column=True)
         o = ctx.buffer("attn_out", (T, H * dv), rt.act_dtype)
         with ops.section("recurrence.norm"):
+            # an output product that sums partial results wants its target zero: this kernel clears it on the side
+            clear = residual if overwrite and residual.dtype == torch.float32 and self.out.needs_zero(T) else None
             ops.gla_finish(raw, self.out_gain, s.norm_eps, proj[:, g_off:g_off + H * dv], o, num_heads=H, value_dim=dv,
-                           gain_per_head=True, gate_sigmoid=True, max_row=gates[2])
+                           gain_per_head=True, gate_sigmoid=True, max_row=gates[2], clear=clear)
+        if clear is not None:
+            ctx.note_cleared()
         with ops.section("recurrence.out"):
-            self.out.accumulate(o, residual, ctx)
+            if overwrite:
+                self.out.store(o, residual, ctx)
+            else:
+                self.out.accumulate(o, residual, ctx)
         return False
 
 

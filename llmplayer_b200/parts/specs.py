@@ -105,11 +105,12 @@ class AttentionSpec:
     unit_norm_eps: Optional[float] = None    # after the rotation, queries and keys are divided by their root mean square per head
     softcap: Optional[float] = None      # score <- softcap * tanh(score / softcap), after the scale
     sink: Optional[str] = None           # tensor [heads]: a learned logit per head in the softmax's denominator, without key or value
+    exact_weights: bool = False          # softmax weights meet the values at float32 precision also on the tensor cores
 
     @property
     def general(self) -> bool:
         return (self.value_dim not in (None, self.head_dim) or any(b is not None for b in (self.q_bias, self.k_bias, self.v_bias))
-                or self.unit_norm_eps is not None or self.softcap is not None or self.sink is not None)
+                or self.unit_norm_eps is not None or self.softcap is not None or self.sink is not None or self.exact_weights)
 
 
 @dataclass(frozen=True)

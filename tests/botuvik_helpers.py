@@ -61,9 +61,9 @@ RAGGED = {
 }
 CONFIGS = {"small": (SMALL, 21, 0.09), "wide": (WIDE, 22, 0.06), "ragged": (RAGGED, 23, 0.1)}
 
-# bfloat16: at most four times the worst error the comparisons of each configuration achieved on a B200 (small: 5.8e-2
-# over six runs of layers whose every sublayer is normed to unit size before it is added; wide 3.3e-2; ragged 1.6e-2)
-BFLOAT16_BOUND = {"small": 8e-2, "wide": 5e-2, "ragged": 4e-2}
+# bfloat16: at most four times the worst error that the comparisons of each configuration achieved on a B200 at all
+# but one position in fifty (see test_botuvik_model.close)
+BFLOAT16_BOUND = {"small": 6e-2, "wide": 4e-2, "ragged": 4e-2}
 ROUTE_CHANNELS = 8          # channels of the stream that carry each token's routing code (see make_model)
 
 

@@ -155,6 +155,13 @@ def test_prompt_attention_with_cap_and_sink(dtype, H, G, hd, length, new):
                               head_dim=hd, scale=scale, window=None, softcap=cap, sinks=sinks)
         lim = 1.5e-2
     check_error(f"capped attention over a prompt, {dtype}", f"{H}/{G} x {hd}, {new} of {length}", rel(out.view(new, H, hd), ref), lim)
+    if dtype == torch.bfloat16:
+        # the weights at float32 precision (a bfloat16 value plus a bfloat16 rest): what is left is the output's rounding
+        fine = torch.empty_like(qd)
+        ops.attention_prefill(qd, fine, pages, table, i32([0, new]), i32([length]), new, num_heads=H, num_kv_heads=G,
+                              head_dim=hd, scale=scale, window=None, softcap=cap, sinks=sinks, exact_weights=True)
+        check_error("capped attention over a prompt, bfloat16, float32 weights", f"{H}/{G} x {hd}, {new} of {length}",
+                    rel(fine.view(new, H, hd), ref), 6e-3)
     # without the sink and the cap the result differs visibly: both take part
     for kw in (dict(softcap=cap, sinks=None), dict(softcap=None, sinks=sinks)):
         other = torch.empty_like(qd)
@@ -232,6 +239,10 @@ def test_decode_attention_in_shares(shares):
                          pages_per_split=per, num_splits=num)
     ref = plain_attention(q.double(), k.double(), v.double(), 0.2, 10.0, sinks.double().cpu(), length - 1)
     check_error("capped decode attention, bfloat16", f"{num} shares", rel(out.view(1, H, hd), ref), 1.5e-2)
+    ops.attention_decode(qd, out, pages, i32([rows]), i32([length]), lambda n, s, d: torch.empty(s, dtype=d, device="cuda"),
+                         num_heads=H, num_kv_heads=G, head_dim=hd, scale=0.2, window=None, softcap=10.0, sinks=sinks,
+                         pages_per_split=per, num_splits=num, exact_weights=True)
+    check_error("capped decode attention, bfloat16, float32 weights", f"{num} shares", rel(out.view(1, H, hd), ref), 6e-3)
 
 
 # --------------------------------------------------------------------------- matrix memory
