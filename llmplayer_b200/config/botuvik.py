@@ -318,8 +318,12 @@ class BotuvikConfig(ArchitectureConfig):
             head=HeadSpec(self.vocab, d, norm=NormSpec(d, eps, "final.norm"), weight="head"), schedule=self.schedule())
 
     def ignorable_tensors(self) -> tuple:
-        # a layer without a feed-forward has no use for the norms around one, should a file carry them
-        return tuple(f"l{i}.{n}" for i, layer in enumerate(self.layers) if layer.mlp is None for n in ("norm2", "norm2b"))
+        # a layer without a feed-forward has no use for the norms around one, nor a model without a loop for the
+        # passes' vectors, should a file carry them
+        spare = [f"l{i}.{n}" for i, layer in enumerate(self.layers) if layer.mlp is None for n in ("norm2", "norm2b")]
+        if self.loop is None:
+            spare.append("loop.step")
+        return tuple(spare)
 
     def describe(self) -> str:
         lines = [f"architecture: {self.architecture}", f"  vocab = {self.vocab}", f"  width = {self.width}",

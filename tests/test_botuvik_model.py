@@ -47,7 +47,8 @@ def reference(model_dir, tokens):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name,length", [("small", 1), ("small", 2), ("small", 97), ("small", 300), ("wide", 33),
-                                         ("wide", 200), ("wide", 321), ("ragged", 3), ("ragged", 270)])
+                                         ("wide", 200), ("wide", 321), ("ragged", 3), ("ragged", 270), ("mixed", 5),
+                                         ("mixed", 140), ("mixed", 290)])
 def test_whole_sequence(tmp_path, name, length, dtype):
     from llmplayer_b200 import Engine
     model_dir = make_model(tmp_path, name, dtype)
@@ -86,7 +87,7 @@ def test_the_stream_after_every_run(tmp_path, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["small", "wide", "ragged"])
+@pytest.mark.parametrize("name", ["small", "wide", "ragged", "mixed"])
 def test_prompt_then_token_by_token(tmp_path, name, dtype):
     """Most of a sequence in one step, the rest one token at a time across a page's border (position 128);
     every decoded position against the whole-sequence plain implementation."""
@@ -125,7 +126,7 @@ def test_portions_of_a_prompt(tmp_path, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["small", "wide", "ragged"])
+@pytest.mark.parametrize("name", ["small", "wide", "ragged", "mixed"])
 def test_unequal_batches_and_reuse(tmp_path, name, dtype):
     """Requests of unequal lengths in one batch, decoded together while the shorter ones end; then new requests
     in the slots and pages that were given back (their state must start at zero); each against itself alone."""
