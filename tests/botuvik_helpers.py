@@ -86,7 +86,7 @@ CONFIGS = {"small": (SMALL, 21, 0.09), "wide": (WIDE, 22, 0.06), "ragged": (RAGG
 
 # bfloat16: at most four times the worst error that the comparisons of each configuration achieved on a B200 at all
 # but one position in fifty (see test_botuvik_model.close)
-BFLOAT16_BOUND = {"small": 6e-2, "wide": 4e-2, "ragged": 4e-2, "mixed": 6e-2}
+BFLOAT16_BOUND = {"small": 6e-2, "wide": 1.2e-2, "ragged": 3.5e-2, "mixed": 4e-2}     # achieved: 4.0e-2, 3.4e-3, 9.6e-3, 1.1e-2
 ROUTE_CHANNELS = 8          # channels of the stream that carry each token's routing code (see make_model)
 
 
