@@ -173,7 +173,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
 // approximation (relative error 2^-22, far below bfloat16's), and the tiles with the most keys
 // (the last ones of a prompt) are started first.
 template <int HD, int ROWS, bool SPLIT = false>
-__global__ void __launch_bounds__(ROWS * 2)
+__global__ void __launch_bounds__(ROWS * 2, SPLIT ? 3 : 1)
 attention_prefill_exact_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
                                const __nv_bfloat16* __restrict__ pages, const int* __restrict__ page_table,
                                int pt_stride, const int* __restrict__ q_start, const int* __restrict__ kv_len, int H,

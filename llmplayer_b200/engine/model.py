@@ -93,7 +93,7 @@ class Model:
         x0 = None
         if self._keeps_embedding:
             x0 = ctx.buffer("embedding_out", (ctx.num_tokens, d), torch.float32)
-            x0.copy_(x)
+            self.embedding.forward(ctx.tokens, x0)          # the rows again, into a buffer that the layers leave alone
         ready = False        # whether the previous block already normed the stream for this one
         for i, run in enumerate(self.runs):
             block = self.blocks[run.layer]
